@@ -1,0 +1,164 @@
+/*
+ * CPU oracle for the RL-Spline-KV feature path, plain C + OpenMP.
+ * TEST INFRASTRUCTURE ONLY: the checker that the CUDA kernels are compared
+ * against and the timed CPU baseline.  The shipped library never links it.
+ *
+ * It restates the algorithm of the reference package's PyTorch oracle
+ * (paths inside the reference project):
+ *   knot interval + B-spline weights  src/sparsespline_ffn/rl_spline_kv_reference.py:88-109
+ *   forward delta gather-sum          src/sparsespline_ffn/rl_spline_kv_reference.py:189-203
+ *   analytic dC / dz_spline, masks    src/sparsespline_ffn/kernels/flash_spline_feature_backward_ref.py:96-150
+ *   base-path gradient, lambda rule   src/sparsespline_ffn/kernels/flash_spline_feature_autograd.py:146-152, 226-242
+ *
+ * Parity is pinned: tests/test_oracle_golden.py checks this file (through
+ * oracle/c_binding.py) against outputs of the reference itself stored under
+ * tests/golden/.
+ *
+ * Inputs are float32 (bf16 tensors are up-cast by the caller, which is exact).
+ * The knot index is computed as the reference computes it in float32:
+ * u = fl(fl(z - lo) * scale), no fused multiply-add.  Sums over keys and over
+ * tokens are accumulated in double.
+ *
+ * Build: gcc -O2 -fopenmp -ffp-contract=off -shared -fPIC spline_kv_oracle.c -o libskv_oracle.so
+ */
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+typedef struct {
+    int bin;          /* knot interval in [0, G-1] */
+    float B[3];       /* forward weights, forward mask applied */
+    float dB[3];      /* derivative weights, clamp mask applied */
+} skvo_basis;
+
+static inline skvo_basis skvo_eval(float z, float lo, float scale, int G)
+{
+    skvo_basis o;
+    volatile float d = z - lo;            /* keep the two roundings separate */
+    float u = d * scale;
+    int in_range = (u >= 0.0f) && (u <= (float)G);
+    int clamp_active = (u >= 0.0f) && (u <= (float)(G - 1));
+    float uc = u;
+    if (!(uc >= 0.0f)) uc = 0.0f;
+    if (uc > (float)(G - 1)) uc = (float)(G - 1);
+    int b = (int)uc;                       /* uc >= 0: truncation is floor */
+    float tau = uc - (float)b;
+    if (tau < 0.0f) tau = 0.0f;
+    if (tau > 1.0f) tau = 1.0f;
+    float omt = 1.0f - tau;
+    float m = in_range ? 1.0f : 0.0f;
+    float c = clamp_active ? 1.0f : 0.0f;
+    o.bin = b;
+    o.B[0] = 0.5f * omt * omt * m;
+    o.B[1] = 0.5f * (1.0f + 2.0f * tau - 2.0f * tau * tau) * m;
+    o.B[2] = 0.5f * tau * tau * m;
+    o.dB[0] = -omt * c;
+    o.dB[1] = (1.0f - 2.0f * tau) * c;
+    o.dB[2] = tau * c;
+    return o;
+}
+
+int skvo_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* bins[N*h] (int32), row-major; z has row stride zs (elements). */
+void skvo_knot_index(const float *z, int64_t zs, int64_t N, int h,
+                     float lo, float scale, int G, int32_t *bins)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n)
+        for (int j = 0; j < h; ++j)
+            bins[n * h + j] = skvo_eval(z[n * zs + j], lo, scale, G).bin;
+}
+
+/* act: 0 = relu_sq, 1 = identity.
+ * a[N*h] (may be NULL) receives phi(z); delta[N*r] receives lambda * delta. */
+void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, int L, int r,
+                  float lo, float scale, float lambda, int act, float *a, float *delta)
+{
+    int G = L - 2;
+#pragma omp parallel
+    {
+        double *acc = (double *)malloc(sizeof(double) * (size_t)r);
+#pragma omp for schedule(static)
+        for (int64_t n = 0; n < N; ++n) {
+            for (int c = 0; c < r; ++c) acc[c] = 0.0;
+            for (int j = 0; j < h; ++j) {
+                float zz = z[n * zs + j];
+                if (a) a[n * h + j] = act == 0 ? (zz > 0.0f ? zz * zz : 0.0f) : zz;
+                skvo_basis e = skvo_eval(zz, lo, scale, G);
+                const float *row = C + ((size_t)j * L + e.bin) * r;
+                double b0 = e.B[0], b1 = e.B[1], b2 = e.B[2];
+                for (int c = 0; c < r; ++c)
+                    acc[c] += b0 * row[c] + b1 * row[r + c] + b2 * row[2 * r + c];
+            }
+            for (int c = 0; c < r; ++c) delta[n * r + c] = (float)((double)lambda * acc[c]);
+        }
+        free(acc);
+    }
+}
+
+/* Backward of f = [phi(z); lambda*delta].
+ *   g_delta[N*r] (row stride gds): gradient w.r.t. the lambda*delta half.
+ *   g_a[N*h] (row stride gas) may be NULL (delta-only operator).
+ *   dz[N*h] float32 out = g_a*phi'(z) + lambda*dz_spline.
+ *   dC[h*L*r] double out = lambda * Phi^T g_delta. */
+void skvo_backward(const float *z, int64_t zs, const float *C,
+                   const float *g_delta, int64_t gds, const float *g_a, int64_t gas,
+                   int64_t N, int h, int L, int r, float lo, float scale, float lambda, int act,
+                   float *dz, double *dC)
+{
+    int G = L - 2;
+    /* dz: parallel over tokens */
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        const float *g = g_delta + n * gds;
+        for (int j = 0; j < h; ++j) {
+            float zz = z[n * zs + j];
+            skvo_basis e = skvo_eval(zz, lo, scale, G);
+            const float *row = C + ((size_t)j * L + e.bin) * r;
+            double s0 = 0.0, s1 = 0.0, s2 = 0.0;
+            for (int c = 0; c < r; ++c) {
+                double gc = g[c];
+                s0 += gc * row[c];
+                s1 += gc * row[r + c];
+                s2 += gc * row[2 * r + c];
+            }
+            double v = (double)lambda * (double)scale * (e.dB[0] * s0 + e.dB[1] * s1 + e.dB[2] * s2);
+            if (g_a) {
+                double dphi = act == 0 ? (zz > 0.0f ? 2.0 * (double)zz : 0.0) : 1.0;
+                v += (double)g_a[n * gas + j] * dphi;
+            }
+            dz[n * h + j] = (float)v;
+        }
+    }
+    /* dC: parallel over keys, every key owns its [L, r] slab */
+#pragma omp parallel for schedule(static)
+    for (int j = 0; j < h; ++j) {
+        double *slab = dC + (size_t)j * L * r;
+        memset(slab, 0, sizeof(double) * (size_t)L * r);
+        for (int64_t n = 0; n < N; ++n) {
+            skvo_basis e = skvo_eval(z[n * zs + j], lo, scale, G);
+            const float *g = g_delta + n * gds;
+            double *row = slab + (size_t)e.bin * r;
+            double b0 = e.B[0], b1 = e.B[1], b2 = e.B[2];
+            for (int c = 0; c < r; ++c) {
+                double gc = g[c];
+                row[c] += b0 * gc;
+                row[r + c] += b1 * gc;
+                row[2 * r + c] += b2 * gc;
+            }
+        }
+        for (size_t i = 0; i < (size_t)L * r; ++i) slab[i] *= (double)lambda;
+    }
+}

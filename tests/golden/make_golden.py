@@ -1,0 +1,118 @@
+"""Generate the golden vectors in this folder by running the reference itself.
+
+Run where the reference source tree is available:
+
+    python tests/golden/make_golden.py --reference-src <reference>/src
+
+It imports the reference's own PyTorch oracle (``flash_spline_feature_reference``,
+``_b2_basis_and_bins``, ``flash_spline_delta_backward_ref`` and the CPU path of
+``FlashSplineFeature`` / ``FlashSplineDelta``), evaluates it in float32 on small
+seeded inputs and stores inputs and outputs in ``spline_kv_golden.npz``.  The
+fixture travels with the repository; the reference does not have to be present
+when the tests run.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def bf16_round(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def cases():
+    g = torch.Generator().manual_seed(0)
+
+    def rn(*shape, scale=1.0):
+        return torch.randn(*shape, generator=g, dtype=torch.float32) * scale
+
+    out = {}
+    # the reference parity harness distribution: z = 2*randn, C = 0.1*randn, grid [-3, 3]
+    out["uniform"] = dict(z=rn(48, 24, scale=2.0), C=rn(24, 10, 8, scale=0.1), lo=-3.0, hi=3.0,
+                          G=8, act="relu_sq", lam=1.0)
+    # production-like: G=20, r=32, grid [-5, 5], lambda warm-up value, bf16-representable inputs
+    out["d20_like"] = dict(z=bf16_round(rn(32, 40, scale=2.5)), C=bf16_round(rn(40, 22, 32, scale=0.02)),
+                           lo=-5.0, hi=5.0, G=20, act="relu_sq", lam=0.25)
+    # skewed and collapsed pre-activations (the reference's backward stress workloads)
+    out["skewed"] = dict(z=rn(40, 16, scale=0.5) + 2.0, C=rn(16, 22, 16, scale=0.1), lo=-3.0, hi=3.0,
+                         G=20, act="relu_sq", lam=1.0)
+    out["collapsed"] = dict(z=rn(40, 16, scale=0.05), C=rn(16, 22, 16, scale=0.1), lo=-3.0, hi=3.0,
+                            G=20, act="identity", lam=0.5)
+    # edge values: knots, grid ends, one ulp either side, far outside, infinities
+    lo, hi, G = -3.0, 3.0, 12
+    knots = torch.linspace(lo, hi, G + 1, dtype=torch.float32)
+    specials = torch.cat([
+        knots,
+        torch.nextafter(knots, torch.full_like(knots, 10.0)),
+        torch.nextafter(knots, torch.full_like(knots, -10.0)),
+        torch.tensor([0.0, -0.0, 2.5, 2.4999998, 2.5000002, 100.0, -100.0, 1e30, -1e30,
+                      float("inf"), float("-inf"), 1e-30, -1e-30], dtype=torch.float32),
+    ])
+    n = specials.numel()
+    h = 6
+    z = specials[:, None].repeat(1, h) + torch.arange(h, dtype=torch.float32)[None, :] * 0.0
+    z[:, 1] = specials.flip(0)
+    z[:, 2] = rn(n, scale=3.0)
+    out["edges"] = dict(z=z, C=rn(h, G + 2, 8, scale=0.1), lo=lo, hi=hi, G=G, act="relu_sq", lam=1.0)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference-src", required=True)
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference_src)
+    from sparsespline_ffn.rl_spline_kv_reference import (  # noqa: E402
+        _b2_basis_and_bins, flash_spline_feature_reference)
+    from sparsespline_ffn.kernels.flash_spline_feature_backward_ref import (  # noqa: E402
+        flash_spline_delta_backward_ref)
+    from sparsespline_ffn.kernels.flash_spline_feature_autograd import (  # noqa: E402
+        flash_spline_delta, flash_spline_feature)
+
+    torch.set_num_threads(1)
+    store = {}
+    gg = torch.Generator().manual_seed(7)
+    for name, c in cases().items():
+        z, C = c["z"], c["C"]
+        N, h = z.shape
+        r = C.shape[-1]
+        lo, hi, G, act, lam = c["lo"], c["hi"], c["G"], c["act"], c["lam"]
+        go = torch.randn(N, h + r, generator=gg, dtype=torch.float32)
+        bins, B0, B1, B2, in_range = _b2_basis_and_bins(z, lo, hi, G)
+        f = flash_spline_feature_reference(z, C, lo, hi, G, activation=act, lambda_scale=lam)
+        # gradients through the reference Function's CPU path (reference recomputation)
+        finite = torch.isfinite(z).all()
+        zt = z.clone().requires_grad_(True)
+        Ct = C.clone().requires_grad_(True)
+        fo = flash_spline_feature(zt, Ct, lo, hi, G, act, lam, use_kernel=False)
+        fo.backward(go)
+        dz, dC = zt.grad.clone(), Ct.grad.clone()
+        # delta-only operator
+        zt2 = z.clone().requires_grad_(True)
+        Ct2 = C.clone().requires_grad_(True)
+        d = flash_spline_delta(zt2, Ct2, lo, hi, G, lam, "triton")
+        d.backward(go[:, h:].contiguous())
+        # analytic backward reference (gradient w.r.t. unscaled delta)
+        dC_an, dzs_an = flash_spline_delta_backward_ref(z, C, go[:, h:].contiguous(), lo, hi, G)
+        rec = dict(z=z, C=C, go=go, bins=bins.to(torch.int32), B=torch.stack([B0, B1, B2]),
+                   in_range=in_range.to(torch.uint8), f=f, dz=dz, dC=dC,
+                   delta_only=d.detach(), delta_dz=zt2.grad, delta_dC=Ct2.grad,
+                   analytic_dC=dC_an, analytic_dz_spline=dzs_an,
+                   meta=torch.tensor([lo, hi, float(G), lam, 0.0 if act == "relu_sq" else 1.0,
+                                      1.0 if bool(finite) else 0.0], dtype=torch.float64))
+        for k, v in rec.items():
+            store[f"{name}/{k}"] = v.detach().numpy()
+    path = os.path.join(HERE, "spline_kv_golden.npz")
+    np.savez_compressed(path, **store)
+    print(path, os.path.getsize(path), "bytes;", len(store), "arrays")
+
+
+if __name__ == "__main__":
+    main()
