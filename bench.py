@@ -1,0 +1,335 @@
+#!/usr/bin/env python
+"""Benchmark of the spline-KV feature operator: forward + backward tokens/s at the d20 shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward and one backward of the feature operator over one batch of synthetic
+pre-activations: N = 65536 tokens per GPU, h = 5120 keys, G = 20 (L = 22), r = 32, bf16, grid
+[-5, 5], lambda = 1 (for more than one GPU: the token-sharded mode, lambda = 0.25 and wider
+pre-activations, with the float32 dC all-reduce over NCCL).  Rank 0 prints one JSON line.
+
+* ``value``: tokens/s of all ranks with inputs resident in HBM, CUDA-event timed, max over ranks.
+* ``e2e``: the same through the public operator with HOST buffers: each step copies z and the
+  upstream gradient from pinned host memory and copies f, dz and dC back.
+* ``roofline``: the slowest of the three main kernels (forward, dz, dC), timed alone with CUDA
+  events in a separate pass of the same length, against the measured dense bf16 peak.
+* ``cpu_baseline``: the CPU oracle (a C/OpenMP port of the reference's algorithm) on a bounded
+  token sample of the same workload, all host threads.
+
+``--impl reference`` times that CPU port alone (rank 0 only) and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "spline-KV fwd+bwd tokens/s @ h=5120,G=20,r=32 bf16"
+SHAPE = dict(N=65536, d=1280, h=5120, G=20, r=32, grid_lo=-5.0, grid_hi=5.0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread:
+            self.thread.join(timeout=2)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                smax.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return None
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_port_tokens_per_s(cfg, seed, target_seconds=12.0):
+    """Forward + backward of the CPU oracle (C/OpenMP port) on a token sample of the workload."""
+    import numpy as np
+    from oracle import c_binding as oc
+    oc.build()
+    h, r, G = cfg["h"], cfg["r"], cfg["G"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    rng = np.random.default_rng(seed)
+
+    def run(n):
+        z = (rng.standard_normal((n, h)) * cfg["z_std"]).astype(np.float32)
+        C = (rng.standard_normal((h, G + 2, r)) * 0.02).astype(np.float32)
+        go = rng.standard_normal((n, h + r)).astype(np.float32)
+        t0 = time.perf_counter()
+        oc.feature_forward(z, C, lo, hi, G, "relu_sq", lam)
+        oc.feature_backward(z, C, go[:, h:], go[:, :h], lo, hi, G, "relu_sq", lam)
+        return time.perf_counter() - t0
+
+    run(64)
+    probe_n = 256
+    t = run(probe_n)
+    n = int(max(256, min(cfg["N"], probe_n * target_seconds / max(t, 1e-6))))
+    n = (n // 256) * 256
+    t = run(n)
+    return n / t, n, t, oc.num_threads()
+
+
+def reference_arm(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals, n, threads = [], 0, 1
+    per_step_target = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        v, n, t, threads = cpu_port_tokens_per_s(cfg, seed=i, target_seconds=per_step_target)
+        if i >= args.warmup:
+            vals.append((v, t))
+    value = statistics.mean(v for v, _ in vals)
+    ms = statistics.mean(t for _, t in vals) * 1e3
+    sample = f"{n} of {cfg['N']} tokens per step at h={cfg['h']}, r={cfg['r']}, G={cfg['G']}; fwd+bwd, float64 accumulate"
+    line = dict(impl="reference", metric=METRIC, value=value, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="f32", data="synthetic", config=cfg_json(cfg, args.gpus),
+                cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=sample),
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def cfg_json(cfg, gpus):
+    return dict(workload=cfg["name"], tokens_per_gpu=cfg["N"], h=cfg["h"], G=cfg["G"], L=cfg["G"] + 2, r=cfg["r"],
+                grid=[cfg["grid_lo"], cfg["grid_hi"]], lambda_scale=cfg["lambda_scale"], z_std=cfg["z_std"],
+                sharding="none" if gpus == 1 else f"tokens x{gpus}, dC all-reduce (float32, NCCL)",
+                l2="inputs larger than L2 (z is 671 MB per GPU)")
+
+
+def make_cfg(gpus):
+    cfg = dict(SHAPE)
+    if gpus == 1:
+        cfg.update(name="d20 production shape, single layer fwd+bwd (config 1)", lambda_scale=1.0, z_std=1.0)
+    else:
+        cfg.update(name="d20 shape token-sharded with dC all-reduce (config 2)", lambda_scale=0.25, z_std=2.0)
+    return cfg
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling of small cases)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    cfg = make_cfg(args.gpus)
+    if args.tokens:
+        cfg["N"] = args.tokens
+        cfg["name"] += f" [reduced to {args.tokens} tokens]"
+    if args.impl == "reference":
+        reference_arm(args, cfg)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from sparsespline_ffn_b200 import _lib, ops, sharded
+    from sparsespline_ffn_b200 import flash_spline_feature
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    _lib.check(lib.skv_device_ok())
+
+    N, d, h, G, r = cfg["N"], cfg["d"], cfg["h"], cfg["G"], cfg["r"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    cgen = torch.Generator(device=dev).manual_seed(99)           # C is replicated: same seed on all ranks
+    x = torch.randn(N, d, generator=gen, device=dev) * cfg["z_std"]
+    W_in = torch.randn(d, h, generator=cgen, device=dev) * (1.0 / d) ** 0.5
+    z = (x @ W_in).to(torch.bfloat16)
+    del x, W_in
+    C = (torch.randn(h, G + 2, r, generator=cgen, device=dev) * 0.02).to(torch.bfloat16)
+    go = torch.randn(N, h + r, generator=gen, device=dev).to(torch.bfloat16)
+    z.requires_grad_(True)
+    C.requires_grad_(True)
+    oor = float(((z.detach().float() < lo) | (z.detach().float() > hi)).float().mean().item())
+
+    def step_device():
+        z.grad = None
+        C.grad = None
+        if world == 1:
+            f = flash_spline_feature(z, C, lo, hi, G, "relu_sq", lam, True)
+        else:
+            f = sharded.token_sharded_spline_feature(z, C, lo, hi, G, "relu_sq", lam)
+        f.backward(go)
+        return f
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """K calls of fn bracketed by barrier + synchronize; ms of the whole region, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = int(lib.skv_kernel_launches())
+    total_ms = timed(step_device, args.steps)
+    launches = int(lib.skv_kernel_launches()) - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_status(dev)
+    ms_per_step = total_ms / args.steps
+    value = world * N / (ms_per_step * 1e-3)
+
+    # ---- per-kernel attribution: forward, dz and dC each timed alone over the same number of steps
+    zd, Cd = z.detach(), C.detach()
+    kern = {}
+    kern["forward"] = timed(lambda: ops.feature_forward(zd, Cd, lo, hi, G, "relu_sq", lam), args.steps) / args.steps
+    kern["dz"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam, need_dC=False),
+                       args.steps) / args.steps
+    kern["dC"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam, need_dz=False),
+                       args.steps) / args.steps
+    impl = ops.resolve_impl(zd, Cd, lo, hi, G)
+    peaks = measured_peaks()
+    dominant = max(kern, key=kern.get)
+    flops = 2.0 * N * h * (G + 2) * r                      # dense-equivalent FLOPs of one of the three GEMMs
+    achieved = flops / (kern[dominant] * 1e-3) / 1e12
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f).get(f"{impl}:{dominant}")
+    roofline = dict(bound="tensor", kernel=f"{impl}:{dominant}", achieved=achieved, peak=peaks["bf16_tflops"],
+                    unit="TFLOP/s", frac=achieved / peaks["bf16_tflops"], traffic=traffic,
+                    peak_source=peaks["source"] + " burst bf16 (kernel timed alone)",
+                    kernel_ms={k: round(v, 4) for k, v in kern.items()},
+                    fwd_bwd_frac_of_tensor_roofline=(3 * flops / (ms_per_step * 1e-3) / 1e12)
+                    / peaks["bf16_tflops_sustained"])
+
+    # ---- end to end through the public operator with host buffers
+    e2e = None
+    if not args.no_e2e:
+        zh = z.detach().cpu().pin_memory()
+        goh = go.cpu().pin_memory()
+        fh = torch.empty((N, h + r), dtype=torch.bfloat16).pin_memory()
+        dzh = torch.empty((N, h), dtype=torch.bfloat16).pin_memory()
+        dCh = torch.empty((h, G + 2, r), dtype=torch.bfloat16).pin_memory()
+        zdev = torch.empty_like(zh, device=dev)
+        godev = torch.empty_like(goh, device=dev)
+
+        def step_e2e():
+            zdev.copy_(zh, non_blocking=True)
+            godev.copy_(goh, non_blocking=True)
+            zz = zdev.requires_grad_(True)
+            zz.grad = None
+            C.grad = None
+            if world == 1:
+                f = flash_spline_feature(zz, C, lo, hi, G, "relu_sq", lam, True)
+            else:
+                f = sharded.token_sharded_spline_feature(zz, C, lo, hi, G, "relu_sq", lam)
+            f.backward(godev)
+            fh.copy_(f.detach(), non_blocking=True)
+            dzh.copy_(zz.grad, non_blocking=True)
+            dCh.copy_(C.grad, non_blocking=True)
+            zdev.requires_grad_(False)
+
+        for _ in range(2):
+            step_e2e()
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_ms = timed(step_e2e, e2e_steps) / e2e_steps
+        h2d = zh.numel() * 2 + goh.numel() * 2
+        d2h = fh.numel() * 2 + dzh.numel() * 2 + dCh.numel() * 2
+        e2e = dict(value=world * N / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
+                   d2h_bytes_per_step=d2h, ms_per_step=e2e_ms)
+        ops.check_status(dev)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, n, t, threads = cpu_port_tokens_per_s(cfg, seed=0)
+        cpu_baseline = dict(value=v, unit="tokens/s", cores=threads, kind="port",
+                            sample=f"{n} of {N} tokens, same h/r/G, fwd+bwd, {t:.1f} s")
+
+    if rank == 0:
+        line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    data="synthetic", config=dict(cfg_json(cfg, world), kernels=impl, out_of_grid_fraction=oor),
+                    clocks=clocks, e2e=e2e, gpu_launches=launches, roofline=roofline, cpu_baseline=cpu_baseline)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

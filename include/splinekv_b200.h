@@ -1,0 +1,130 @@
+/*
+ * splinekv_b200 -- C ABI of the B200 (sm_100a) implementation of the RL-Spline-KV
+ * feature operator:
+ *
+ *   forward    f = [ phi(z) ; lambda * delta ],   delta[n,:] = sum_j sum_{k<3} B_k(z[n,j]) * C[j, bin(z[n,j]) + k, :]
+ *   backward   dz = g_a * phi'(z) + lambda * scale * sum_k B_k'(z) <g_delta, C[j, bin+k, :]>
+ *              dC = lambda * Phi(z)^T g_delta
+ *
+ * z is [N, h] (tokens x keys), C is [h, L, r] with L = G + 2 knot rows, outputs are in
+ * the dtype of z.  Every entry point takes plain device pointers, sizes and a CUDA stream
+ * handle (cudaStream_t passed as void*); none of them allocates, frees, synchronises or
+ * throws.  They enqueue work on the given stream and return 0 or a negative SKV_ERR_* code.
+ *
+ * Each declaration names the interface of the reference project it replaces
+ * (paths inside that project).
+ */
+#ifndef SPLINEKV_B200_H
+#define SPLINEKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SKV_ABI_VERSION 1
+
+enum skv_error {
+  SKV_OK = 0,
+  SKV_ERR_NULL = -1,        /* a required pointer is NULL */
+  SKV_ERR_SHAPE = -2,       /* N, h, L, r out of range, or L < 4 */
+  SKV_ERR_UNSUPPORTED = -3, /* dtype / activation / impl not supported for this shape */
+  SKV_ERR_ALIGN = -4,       /* pointer or stride alignment the chosen kernel needs is not met */
+  SKV_ERR_SCRATCH = -5,     /* scratch buffer missing or smaller than skv_scratch_bytes() */
+  SKV_ERR_DEVICE = -6,      /* current device is not compute capability 10.x */
+  SKV_ERR_LAUNCH = -7       /* a kernel launch failed (cudaGetLastError) */
+};
+
+enum skv_dtype { SKV_BF16 = 0, SKV_F32 = 1 };
+enum skv_activation { SKV_ACT_RELU_SQ = 0, SKV_ACT_IDENTITY = 1 };
+/* SKV_IMPL_AUTO picks the tcgen05 kernels when the shape is eligible (bf16, r a multiple of 16
+ * up to 128, even L, h a multiple of 8, 16-byte aligned rows) and the CUDA-core kernels otherwise. */
+enum skv_impl { SKV_IMPL_AUTO = 0, SKV_IMPL_SIMT = 1, SKV_IMPL_TCGEN05 = 2 };
+enum skv_op { SKV_OP_FORWARD = 0, SKV_OP_BACKWARD = 1 };
+
+/* Problem description shared by all entry points.  `scale` is float32(G / (grid_hi - grid_lo))
+ * with the division done in double by the caller, as the reference's Python wrappers do
+ * (src/sparsespline_ffn/cuda_ext/__init__.py:334-352, 529-555). */
+typedef struct skv_problem {
+  int64_t N;           /* tokens */
+  int32_t h;           /* keys */
+  int32_t L;           /* knot rows per key, = G + 2 */
+  int32_t r;           /* code dimension */
+  float grid_lo;
+  float scale;
+  float lambda_scale;
+  int32_t activation;  /* enum skv_activation */
+  int32_t dtype;       /* enum skv_dtype: dtype of z, C, grad_out, f, dz */
+  int32_t impl;        /* enum skv_impl */
+  int32_t delta_f32;   /* forward only: 1 = write lambda*delta as float32 whatever dtype is (the
+                          key-sharded mode sums partial residuals across GPUs in float32) */
+} skv_problem;
+
+/* ABI version of the loaded library (SKV_ABI_VERSION). */
+int skv_abi_version(void);
+
+/* Human-readable text for a SKV_ERR_* code. */
+const char *skv_error_string(int code);
+
+/* 0 when the current CUDA device can run this library (compute capability 10.x), else SKV_ERR_DEVICE.
+ * Replaces the capability gates of the reference loaders (src/sparsespline_ffn/cuda_ext/__init__.py:31-60). */
+int skv_device_ok(void);
+
+/* Which kernels SKV_IMPL_AUTO resolves to for this problem: SKV_IMPL_SIMT or SKV_IMPL_TCGEN05
+ * (negative SKV_ERR_* when the problem is invalid).  Replaces the eligibility tests of
+ * FlashSplineFeature.forward (src/sparsespline_ffn/kernels/flash_spline_feature_autograd.py:64-82). */
+int skv_resolve_impl(const skv_problem *p);
+
+/* Bytes of caller-owned scratch that op (enum skv_op) needs for this problem.  The reference
+ * kernels allocate theirs internally (src/sparsespline_ffn/cuda_ext/spline_kv_fwd_v11.cu:372-375,
+ * src/sparsespline_ffn/cuda_ext/spline_kv_bwd_wgmma_v5.cu:588-598). */
+size_t skv_scratch_bytes(const skv_problem *p, int op);
+
+/* Forward.  Replaces spline_kv_fwd_cuda / spline_kv_fwd_v11_cuda
+ * (src/sparsespline_ffn/cuda_ext/__init__.py:529-555, src/sparsespline_ffn/cuda_ext/spline_kv_fwd_v11.cu:349-402)
+ * and the Triton forward flash_spline_feature_forward
+ * (src/sparsespline_ffn/kernels/triton_flash_spline_feature.py:273-369).
+ *   z          [N, h], row stride z_stride elements, unit inner stride
+ *   C          [h, L, r] contiguous
+ *   act_out    [N, h] phi(z), row stride act_stride; NULL for the delta-only operator
+ *   delta_out  [N, r] lambda*delta, row stride delta_stride in elements of its own type (for the
+ *              feature operator pass &f[0][h] and stride h + r so that both halves land in one
+ *              tensor); float32 when p->delta_f32 is set, else the dtype of z
+ *   status     optional device int32; a kernel writes a non-zero code there if one of its
+ *              bounded waits ran out (results are then invalid) */
+int skv_feature_forward(const skv_problem *p, const void *z, int64_t z_stride, const void *C,
+                        void *act_out, int64_t act_stride, void *delta_out, int64_t delta_stride,
+                        void *scratch, size_t scratch_bytes, int32_t *status, void *stream);
+
+/* Backward.  Replaces spline_kv_bwd_wgmma_cuda(_fused) / spline_kv_bwd_wgmma_v5_cuda
+ * (src/sparsespline_ffn/cuda_ext/spline_kv_bwd_wgmma.cu:508-584,
+ * src/sparsespline_ffn/cuda_ext/spline_kv_bwd_wgmma_v5.cu:553-621), the Triton backward
+ * flash_spline_delta_backward_v3 (src/sparsespline_ffn/kernels/triton_flash_spline_feature.py:1294-1331)
+ * and the elementwise tail of FlashSplineFeature.backward
+ * (src/sparsespline_ffn/kernels/flash_spline_feature_autograd.py:146-152, 226-242).
+ *   g_act    [N, h] gradient of the phi(z) half, row stride gact_stride; NULL for delta-only
+ *   g_delta  [N, r] gradient of the lambda*delta half (NOT pre-multiplied by lambda)
+ *   dz       [N, h] out, dtype of z; NULL to skip
+ *   dC_f32   [h, L, r] float32 out (overwritten, not accumulated); NULL to skip
+ *   dC_cast  optional [h, L, r] copy of dC in the dtype of C */
+int skv_feature_backward(const skv_problem *p, const void *z, int64_t z_stride, const void *C,
+                         const void *g_act, int64_t gact_stride, const void *g_delta, int64_t gdelta_stride,
+                         void *dz, int64_t dz_stride, float *dC_f32, void *dC_cast,
+                         void *scratch, size_t scratch_bytes, int32_t *status, void *stream);
+
+/* Knot-interval index of every z[n, j] as int32 [N, h] (contiguous), computed by the same device
+ * function all kernels use.  Lets a caller check indices bit for bit against
+ * _b2_basis_and_bins (src/sparsespline_ffn/rl_spline_kv_reference.py:88-109). */
+int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_t *bins, void *stream);
+
+/* Number of kernels this library has launched in this process so far (host-side counter).  No
+ * counterpart in the reference; benchmarks use the difference around a timed region to report
+ * how many of the library's own kernels ran inside it. */
+uint64_t skv_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPLINEKV_B200_H */

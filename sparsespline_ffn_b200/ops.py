@@ -1,0 +1,193 @@
+"""Tensor-level entry points over the C ABI: allocate outputs and scratch with torch, pass raw
+device pointers and the current stream to ``libsplinekv_b200.so``.
+
+These are the functions the autograd operators and the sharded wrappers call.  They never fall
+back to eager PyTorch: a CPU tensor, a missing library or a non-B200 device raises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.bfloat16: _lib.SKV_BF16, torch.float32: _lib.SKV_F32}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def grid_scale(grid_lo: float, grid_hi: float, G: int) -> float:
+    """``G / (hi - lo)`` in double, as the reference's wrappers compute it
+    (src/sparsespline_ffn/cuda_ext/__init__.py:551); the library rounds it to float32."""
+    return float(G) / (float(grid_hi) - float(grid_lo))
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels write to when a bounded wait runs out (0 = healthy)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = t
+    return t
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait."""
+    v = int(status_word(device).item())
+    if v != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f"splinekv_b200 kernel reported device status {v:#x} (a bounded wait ran out)")
+
+
+def _problem(z: torch.Tensor, C: torch.Tensor, grid_lo, grid_hi, G, activation, lambda_scale, impl) -> _lib.Problem:
+    if z.dim() != 2:
+        raise ValueError(f"z must be 2D [N, h], got {tuple(z.shape)}")
+    if C.dim() != 3:
+        raise ValueError(f"C must be 3D [h, L, r], got {tuple(C.shape)}")
+    N, h = z.shape
+    hC, L, r = C.shape
+    if hC != h:
+        raise ValueError(f"C[0]={hC} != h={h}")
+    if L != G + 2:
+        raise ValueError(f"L={L} should equal G+spline_order={G + 2}")
+    if not float(grid_hi) > float(grid_lo):
+        raise ValueError(f"grid_hi {grid_hi} <= grid_lo {grid_lo}")
+    if activation not in _lib.SKV_ACT:
+        raise ValueError(f"activation {activation!r} is not supported by the sm_100a kernels "
+                         f"(supported: {sorted(_lib.SKV_ACT)})")
+    if impl not in _lib.SKV_IMPL:
+        raise ValueError(f"impl must be one of {sorted(_lib.SKV_IMPL)}, got {impl!r}")
+    if not z.is_cuda or not C.is_cuda:
+        raise RuntimeError("CUDA-only: splinekv_b200 has no CPU path (z and C must be CUDA tensors)")
+    if z.device != C.device:
+        raise RuntimeError(f"z is on {z.device} but C is on {C.device}")
+    if z.dtype not in _DTYPES:
+        raise RuntimeError(f"unsupported dtype {z.dtype}: the sm_100a kernels take bfloat16 or float32")
+    return _lib.Problem(N=N, h=h, L=L, r=r, grid_lo=float(grid_lo), scale=grid_scale(grid_lo, grid_hi, G),
+                        lambda_scale=float(lambda_scale), activation=_lib.SKV_ACT[activation],
+                        dtype=_DTYPES[z.dtype], impl=_lib.SKV_IMPL[impl])
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """A view or copy of a 2-D tensor with unit inner stride (any row stride is passed through)."""
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1]:
+        return t
+    return t.contiguous()
+
+
+def _ptr(t: torch.Tensor | None):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _scratch(lib, p: _lib.Problem, op: int, device) -> tuple[torch.Tensor | None, int]:
+    need = int(lib.skv_scratch_bytes(ctypes.byref(p), op))
+    if need == 0:
+        return None, 0
+    return torch.empty(need, dtype=torch.uint8, device=device), need
+
+
+def resolve_impl(z, C, grid_lo, grid_hi, G, impl="auto") -> str:
+    """Name of the kernel family the library would use for this problem: 'simt' or 'tcgen05'."""
+    lib = _lib.load()
+    p = _problem(z, C, grid_lo, grid_hi, G, "relu_sq", 1.0, impl)
+    code = lib.skv_resolve_impl(ctypes.byref(p))
+    if code < 0:
+        _lib.check(code)
+    return {1: "simt", 2: "tcgen05"}[code]
+
+
+def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0, with_base=True,
+                    impl="auto", out: torch.Tensor | None = None, delta_f32: bool = False):
+    """``[phi(z); lambda*delta]`` as ``[N, h+r]`` (``with_base``) or ``lambda*delta`` as ``[N, r]``.
+
+    With ``delta_f32`` the residual comes back in float32 whatever the dtype of ``z`` (the
+    key-sharded mode sums partial residuals across GPUs before the one rounding to bf16); the two
+    halves then cannot share a tensor, so the result is ``(phi(z) or None, delta_f32)``."""
+    lib = _lib.load()
+    C = C.to(z.dtype) if C.dtype != z.dtype else C
+    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, impl)
+    z = _rows(z)
+    C = C.contiguous()
+    N, h, r = p.N, p.h, p.r
+    p.delta_f32 = 1 if delta_f32 else 0
+    with torch.cuda.device(z.device):
+        if delta_f32:
+            act = torch.empty((N, h), dtype=z.dtype, device=z.device) if with_base else None
+            delta = torch.empty((N, r), dtype=torch.float32, device=z.device)
+            act_ptr, act_stride = _ptr(act), h
+            delta_ptr, delta_stride = _ptr(delta), r
+            result = (act, delta)
+        else:
+            width = h + r if with_base else r
+            f = out if out is not None else torch.empty((N, width), dtype=z.dtype, device=z.device)
+            if tuple(f.shape) != (N, width) or f.dtype != z.dtype or f.stride(1) != 1:
+                raise ValueError("out must be [N, width] in the dtype of z with unit inner stride")
+            act_ptr = ctypes.c_void_p(f.data_ptr()) if with_base else None
+            delta_ptr = ctypes.c_void_p(f.data_ptr() + (h * f.element_size() if with_base else 0))
+            act_stride = delta_stride = f.stride(0)
+            result = f
+        scratch, nbytes = _scratch(lib, p, _lib.SKV_OP_FORWARD, z.device)
+        code = lib.skv_feature_forward(
+            ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), act_ptr, act_stride, delta_ptr, delta_stride,
+            _ptr(scratch), nbytes, _ptr(status_word(z.device)),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(code)
+    return result
+
+
+def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0,
+                     with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True):
+    """Gradients for ``grad_out`` of :func:`feature_forward`.
+
+    Returns ``(dz or None, dC_f32 or None, dC_cast or None)``; ``dC_cast`` (dtype of ``C``) is only
+    produced for bf16 problems when ``cast_dC`` is set.
+    """
+    lib = _lib.load()
+    C_in_dtype = C.dtype
+    C = C.to(z.dtype) if C.dtype != z.dtype else C
+    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, impl)
+    z = _rows(z)
+    C = C.contiguous()
+    N, h, r, L = p.N, p.h, p.r, p.L
+    width = h + r if with_base else r
+    if tuple(grad_out.shape) != (N, width):
+        raise ValueError(f"grad_out must be [N, {width}], got {tuple(grad_out.shape)}")
+    go = _rows(grad_out.to(z.dtype) if grad_out.dtype != z.dtype else grad_out)
+    with torch.cuda.device(z.device):
+        dz = torch.empty((N, h), dtype=z.dtype, device=z.device) if need_dz else None
+        dC = torch.empty((h, L, r), dtype=torch.float32, device=z.device) if need_dC else None
+        dC_cast = None
+        if need_dC and cast_dC and z.dtype != torch.float32:
+            dC_cast = torch.empty((h, L, r), dtype=z.dtype, device=z.device)
+        scratch, nbytes = _scratch(lib, p, _lib.SKV_OP_BACKWARD, z.device)
+        esz = go.element_size()
+        gact_ptr = ctypes.c_void_p(go.data_ptr()) if with_base else None
+        gdelta_ptr = ctypes.c_void_p(go.data_ptr() + (h * esz if with_base else 0))
+        code = lib.skv_feature_backward(
+            ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), gact_ptr, go.stride(0), gdelta_ptr, go.stride(0),
+            _ptr(dz), h, _ptr(dC), _ptr(dC_cast), _ptr(scratch), nbytes, _ptr(status_word(z.device)),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(code)
+    if dC_cast is not None and dC_cast.dtype != C_in_dtype:
+        dC_cast = None
+    return dz, dC, dC_cast
+
+
+def knot_index(z, grid_lo, grid_hi, G) -> torch.Tensor:
+    """int32 ``[N, h]`` knot-interval indices as the kernels compute them."""
+    lib = _lib.load()
+    if z.dim() != 2 or not z.is_cuda:
+        raise ValueError("z must be a 2D CUDA tensor")
+    if z.dtype not in _DTYPES:
+        raise RuntimeError(f"unsupported dtype {z.dtype}")
+    z = _rows(z)
+    N, h = z.shape
+    p = _lib.Problem(N=N, h=h, L=G + 2, r=1, grid_lo=float(grid_lo), scale=grid_scale(grid_lo, grid_hi, G),
+                     lambda_scale=1.0, activation=0, dtype=_DTYPES[z.dtype], impl=1)
+    with torch.cuda.device(z.device):
+        bins = torch.empty((N, h), dtype=torch.int32, device=z.device)
+        code = lib.skv_knot_index(ctypes.byref(p), _ptr(z), z.stride(0), _ptr(bins),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(code)
+    return bins
