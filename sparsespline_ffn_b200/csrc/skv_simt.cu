@@ -306,7 +306,9 @@ DcPlan plan_dc(const skv_problem& p, int num_sms) {
   if (splits > 16) splits = 16;
   if (splits < 1) splits = 1;
   d.tokens_per_split = cdiv64(cdiv64(p.N, splits), d.TT) * d.TT;
+  if (d.tokens_per_split < d.TT) d.tokens_per_split = d.TT;
   d.splits = (int)cdiv64(p.N, d.tokens_per_split);
+  if (d.splits < 1) d.splits = 1;
   return d;
 }
 
