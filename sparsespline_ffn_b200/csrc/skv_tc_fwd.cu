@@ -1,0 +1,382 @@
+// tcgen05 forward of the spline-KV feature operator (bf16 I/O, r a multiple of 16 up to 128,
+// even L, h a multiple of 8).
+//
+//   delta[n, c] = sum_j sum_b Phi[n, (j,b)] * C[j, b, c]
+//
+// is computed as a dense GEMM on the 5th-generation tensor cores: the expanded basis Phi (three
+// non-zero weights per key, at knot rows bin..bin+2) is built per token in shared memory as f16,
+// the code table is staged by TMA bulk copies from an f16 image in the canonical operand layout,
+// and tcgen05.mma accumulates 128-token x r tiles in tensor memory in float32.
+//
+// Launch shape: grid = (token tiles of 128*GROUPS tokens, key splits).  A CTA walks its keys in
+// chunks of 8 (K extent 8*L per chunk) through a two-stage ring:
+//   warps 0..4*GROUPS-1  producers, one thread per token: read 8 pre-activations, write the
+//                        ReLU^2 half of the output, compute knot interval and weights in
+//                        registers, store the two non-zero 32-bit words of the Phi row segment;
+//                        after the last chunk they read the accumulator from tensor memory and
+//                        store the float32 partial residual of this key split
+//   warp 4*GROUPS        lane 0 issues the MMAs of each chunk and commits to the ring barriers
+//   warp 4*GROUPS+1      lane 0 issues the bulk copies of the code-table image
+// A small second kernel sums the key splits, applies lambda and casts.
+//
+// Every mbarrier wait is bounded (skv_tc_common.cuh); a timed-out wait sets the status word and
+// lets the CTA drain.
+#include "skv_tc_common.cuh"
+
+namespace skv {
+namespace tc {
+namespace {
+
+constexpr int kStages = 2;
+constexpr int kChunkKeys = 8;
+constexpr int kPlanSMs = 148;                 // B200; only used to balance the launch shape
+constexpr size_t kSmemLimit = 220 * 1024;
+
+struct FwdParams {
+  const __nv_bfloat16* z;
+  int64_t zs;
+  __nv_bfloat16* act_out;
+  int64_t as;
+  const __half* cimg;       // [h/8][8L/8][r/8][8][8] f16 image of C
+  float* partial;           // [splits][N][r]
+  int64_t N;
+  int h, L, r;
+  GridParams g;
+  int act;
+  int chunks_total, chunks_per_split;
+  int32_t* status;
+  uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
+};
+
+__device__ __forceinline__ uint32_t word_off(uint32_t w) { return (w >> 2) * 2048u + (w & 3u) * 4u; }
+
+template <int GROUPS>
+__global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const FwdParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int L = P.L, r = P.r;
+  const uint32_t phi_bytes = (uint32_t)L * 2048u;                 // 128 tokens x 8L f16
+  const uint32_t c_bytes = (uint32_t)(kChunkKeys * L * r * 2);
+  uint8_t* phi_base = smem;                                        // [stage][group][phi_bytes]
+  uint8_t* c_base = smem + (size_t)kStages * GROUPS * phi_bytes;   // [stage][c_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(c_base + (size_t)kStages * c_bytes);
+  uint64_t* full = bars;                          // [stage][group]   producers -> MMA
+  uint64_t* empty = full + kStages * GROUPS;      // [stage][group]   MMA -> producers
+  uint64_t* cfull = empty + kStages * GROUPS;     // [stage]          TMA -> MMA
+  uint64_t* cempty = cfull + kStages;             // [stage]          MMA -> TMA
+  uint64_t* done = cempty + kStages;              // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunk_begin = blockIdx.y * P.chunks_per_split;
+  const int nch = min(P.chunks_per_split, P.chunks_total - chunk_begin);
+  const int64_t tile_base = (int64_t)blockIdx.x * (128 * GROUPS);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < (uint32_t)(GROUPS * r)) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages * GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, 1); }
+    mbar_init(done, 1);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  // zero both Phi stages once; afterwards producers clear exactly the words they wrote
+  {
+    uint4* p = reinterpret_cast<uint4*>(phi_base);
+    const uint32_t n16 = kStages * GROUPS * phi_bytes / 16;
+    for (uint32_t i = tid; i < n16; i += blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (warp == 4 * GROUPS) tmem_alloc(tmem_slot, tmem_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4 * GROUPS) {
+    // ------------------------------------------------------------------ producers / epilogue
+    const int grp = warp >> 2;
+    const int t = tid & 127;
+    const int64_t n = tile_base + grp * 128 + t;
+    const bool valid = n < P.N;
+    const uint32_t t_off = (uint32_t)(t & 7) * 16u + (uint32_t)(t >> 3) * 128u;
+    const __nv_bfloat16* zrow = P.z + (valid ? n : 0) * P.zs + (int64_t)chunk_begin * kChunkKeys;
+    __nv_bfloat16* arow = P.act_out ? P.act_out + (valid ? n : 0) * P.as + (int64_t)chunk_begin * kChunkKeys : nullptr;
+    const uint32_t halfL = (uint32_t)L >> 1;
+    uint32_t saved[kStages][2] = {{0, 0}, {0, 0}};
+    uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
+
+    auto chunk_body = [&](int ci, int s, uint32_t(&sv)[2]) {
+      const uint4 zc = znext;
+      if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
+      const uint32_t row = smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes) + t_off;
+      if (ci >= kStages) {
+        mbar_wait(empty + s * GROUPS + grp, (uint32_t)((ci / kStages) - 1) & 1u, abort_flag, P.status,
+                  kStatusTimeoutFwd);
+        if (valid) {
+#pragma unroll
+          for (int q = 0; q < kChunkKeys; ++q) {
+            const uint32_t w0 = (sv[q >> 2] >> ((q & 3) * 8)) & 0xffu;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(0u) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(0u) : "memory");
+          }
+        }
+      }
+      if (valid) {
+        const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
+        uint32_t aw[4];
+        uint32_t nsv[2] = {0, 0};
+#pragma unroll
+        for (int q = 0; q < kChunkKeys; ++q) {
+          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+          const Knot k = knot_of(zz, P.g);
+          float B0, B1, B2;
+          basis_weights(k, B0, B1, B2);
+          const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
+          const bool odd = (k.bin & 1) != 0;
+          const uint32_t x0 = odd ? (p01 << 16) : p01;
+          const uint32_t x1 = odd ? __funnelshift_r(p01, p2, 16) : p2;
+          const uint32_t w0 = (uint32_t)q * halfL + ((uint32_t)k.bin >> 1);
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(x0) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(x1) : "memory");
+          nsv[q >> 2] |= w0 << ((q & 3) * 8);
+          const float a = act_fwd(zz, P.act);
+          if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
+          else aw[q >> 1] = __float_as_uint(a);
+        }
+        sv[0] = nsv[0];
+        sv[1] = nsv[1];
+        if (arow) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+      }
+      fence_async_smem();
+      mbar_arrive(full + s * GROUPS + grp);
+    };
+
+    for (int ci = 0; ci < nch; ci += kStages) {
+      chunk_body(ci, 0, saved[0]);
+      if (ci + 1 < nch) chunk_body(ci + 1, 1, saved[1]);
+    }
+
+    // epilogue: accumulator -> float32 partial of this key split
+    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    tc_fence_after();
+    float* prow = P.partial + ((size_t)blockIdx.y * P.N + (valid ? n : 0)) * r;
+    const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(grp * r);
+    for (int c0 = 0; c0 < r; c0 += 16) {
+      float v[16];
+      tmem_ld16(taddr + c0, v);
+      if (valid) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4)
+          *reinterpret_cast<float4*>(prow + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      }
+    }
+    tc_fence_before();
+  } else if (warp == 4 * GROUPS) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(0, 0, 0, 1, 128, r);
+      const int ksteps = kChunkKeys * L / 16;
+      for (int ci = 0; ci < nch; ++ci) {
+        const int s = ci % kStages;
+        const uint32_t par = (uint32_t)(ci / kStages) & 1u;
+        mbar_wait(cfull + s, par, abort_flag, P.status, kStatusTimeoutFwd);
+        const uint32_t b_addr = smem_u32(c_base + (size_t)s * c_bytes);
+        for (int grp = 0; grp < GROUPS; ++grp) {
+          mbar_wait(full + s * GROUPS + grp, par, abort_flag, P.status, kStatusTimeoutFwd);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes);
+          for (int ks = 0; ks < ksteps; ++ks) {
+            const uint64_t ad = smem_desc(a_addr + (uint32_t)ks * 2u * 2048u, P.a_lbo, P.a_sbo);
+            const uint64_t bd = smem_desc(b_addr + (uint32_t)ks * 2u * (uint32_t)(r / 8) * 128u, P.b_lbo, P.b_sbo);
+            umma_f16(tmem_base + (uint32_t)(grp * r), ad, bd, idesc, (ci > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(empty + s * GROUPS + grp);
+        }
+        umma_commit(cempty + s);
+      }
+      umma_commit(done);
+    }
+  } else {
+    // ------------------------------------------------------------------ code-table loader
+    if (lane == 0) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(P.cimg) + (size_t)chunk_begin * c_bytes;
+      for (int ci = 0; ci < nch; ++ci) {
+        const int s = ci % kStages;
+        if (ci >= kStages)
+          mbar_wait(cempty + s, (uint32_t)((ci / kStages) - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(cfull + s, c_bytes);
+        bulk_g2s(c_base + (size_t)s * c_bytes, src + (size_t)ci * c_bytes, c_bytes, cfull + s);
+      }
+      // all copies issued have been consumed by the MMA warp unless the CTA is draining after a
+      // timeout; in that case give copies still in flight time to land before the CTA exits
+      if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 4 * GROUPS) {
+    // the accumulator has been read (or the CTA is draining): make sure no MMA is still running
+    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    tc_fence_after();
+    tmem_free(tmem_base, tmem_cols);
+  }
+}
+
+// C [h][L][r] bf16 -> f16 image: per 8-key chunk the [8L x r] tile as 8x8 core matrices,
+// core (kg, cg) at ((kg * r/8 + cg) * 128) bytes, row k%8 at 16 bytes, channel c%8 at 2 bytes.
+__global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int r) {
+  const int rows_per_chunk = kChunkKeys * L;
+  const int cgs = r / 8;
+  const size_t pieces = (size_t)h * L * cgs;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (size_t)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % cgs);
+    const size_t rowg = i / cgs;                       // global (j, b) row
+    const int chunk = (int)(rowg / rows_per_chunk);
+    const int k = (int)(rowg % rows_per_chunk);
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(C + rowg * r + cg * 8));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o[q] = pack_h2(bf_lo(w[q]), bf_hi(w[q]));
+    __half* dst = img + (size_t)chunk * rows_per_chunk * r + ((size_t)(k >> 3) * cgs + cg) * 64 + (k & 7) * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <typename TD>
+__global__ void tc_finalize_kernel(const float* __restrict__ partial, int splits, int64_t N, int r, float lambda,
+                                   TD* __restrict__ out, int64_t ds) {
+  const int64_t total = N * r;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float s = 0.0f;
+    for (int k = 0; k < splits; ++k) s += partial[(size_t)k * total + i];
+    st_f32<TD>(out + (i / r) * ds + (i % r), lambda * s);
+  }
+}
+
+struct FwdPlan {
+  int groups, splits, chunks_per_split;
+  size_t smem;
+};
+
+size_t fwd_smem(int groups, int L, int r) {
+  return (size_t)kStages * groups * L * 2048 + (size_t)kStages * kChunkKeys * L * r * 2 + 256;
+}
+
+bool plan_forward(const skv_problem& p, FwdPlan* out) {
+  int groups = 0;
+  if (fwd_smem(2, p.L, p.r) <= kSmemLimit) groups = 2;
+  else if (fwd_smem(1, p.L, p.r) <= kSmemLimit) groups = 1;
+  if (!groups) return false;
+  const int chunks = p.h / kChunkKeys;
+  const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
+  int best = 1;
+  double best_eff = 0.0;
+  const int max_splits = chunks >= 16 ? (chunks / 8 < 16 ? chunks / 8 : 16) : 1;
+  for (int ks = 1; ks <= max_splits; ++ks) {
+    const double waves = (double)(tiles > 0 ? tiles : 1) * ks / kPlanSMs;
+    const double eff = waves / (double)(int64_t)(waves + 0.999999);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = ks; }
+  }
+  out->groups = groups;
+  out->splits = best;
+  out->chunks_per_split = (chunks + best - 1) / best;
+  out->splits = (chunks + out->chunks_per_split - 1) / out->chunks_per_split;
+  out->smem = fwd_smem(groups, p.L, p.r);
+  return true;
+}
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+}  // namespace
+
+bool fwd_eligible(const skv_problem& p) {
+  if (p.dtype != SKV_BF16) return false;
+  if (p.r % 16 || p.r < 16 || p.r > 128) return false;
+  if (p.L % 2 || p.L < 4 || p.L > 64) return false;
+  if (p.h % kChunkKeys) return false;
+  FwdPlan f;
+  return plan_forward(p, &f);
+}
+
+size_t cimg_bytes(const skv_problem& p) { return align256((size_t)p.h * p.L * p.r * sizeof(__half)); }
+
+size_t fwd_scratch_bytes(const skv_problem& p) {
+  FwdPlan f;
+  if (!plan_forward(p, &f)) return 0;
+  return cimg_bytes(p) + align256((size_t)f.splits * (p.N > 0 ? p.N : 1) * p.r * sizeof(float));
+}
+
+int launch_pack_c(const LaunchCtx& c, const void* C, void* img) {
+  const size_t pieces = (size_t)c.p.h * c.p.L * (c.p.r / 8);
+  const unsigned grid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
+  tc_pack_c_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, (__half*)img, c.p.h, c.p.L, c.p.r);
+  note_launches(1);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_LAUNCH;
+}
+
+int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* act_out, int64_t as,
+            void* delta_out, int64_t ds, void* scratch, size_t scratch_bytes) {
+  const skv_problem& p = c.p;
+  FwdPlan f;
+  if (!plan_forward(p, &f)) return SKV_ERR_UNSUPPORTED;
+  if (scratch_bytes < fwd_scratch_bytes(p)) return SKV_ERR_SCRATCH;
+  __half* img = reinterpret_cast<__half*>(scratch);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + cimg_bytes(p));
+  if (int e = launch_pack_c(c, C, img)) return e;
+
+  FwdParams P;
+  P.z = (const __nv_bfloat16*)z;
+  P.zs = zs;
+  P.act_out = (__nv_bfloat16*)act_out;
+  P.as = as;
+  P.cimg = img;
+  P.partial = partial;
+  P.N = p.N;
+  P.h = p.h;
+  P.L = p.L;
+  P.r = p.r;
+  P.g = c.g;
+  P.act = p.activation;
+  P.chunks_total = p.h / kChunkKeys;
+  P.chunks_per_split = f.chunks_per_split;
+  P.status = c.status;
+  // A: Phi tile, K-major; core matrices of 8 tokens x 8 k: 128 B apart along tokens, 2048 B along k
+  P.a_lbo = 2048;
+  P.a_sbo = 128;
+  // B: code-table chunk, N(=channel)-major; core matrices 128 B apart along channels, r/8*128 B along k
+  P.b_lbo = (uint32_t)(p.r / 8) * 128u;
+  P.b_sbo = 128;
+
+  const int64_t tiles = (p.N + 128 * f.groups - 1) / (128 * f.groups);
+  dim3 grid((unsigned)tiles, (unsigned)f.splits);
+  cudaError_t err;
+  if (f.groups == 2) {
+    err = cudaFuncSetAttribute(tc_forward_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem);
+    if (err == cudaSuccess) tc_forward_kernel<2><<<grid, 128 * 2 + 64, f.smem, c.stream>>>(P);
+  } else {
+    err = cudaFuncSetAttribute(tc_forward_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem);
+    if (err == cudaSuccess) tc_forward_kernel<1><<<grid, 128 + 64, f.smem, c.stream>>>(P);
+  }
+  note_launches(1);
+  if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }
+
+  const int64_t total = p.N * p.r;
+  const unsigned fgrid = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+  if (p.delta_f32)
+    tc_finalize_kernel<float><<<fgrid, 256, 0, c.stream>>>(partial, f.splits, p.N, p.r, p.lambda_scale,
+                                                           (float*)delta_out, ds);
+  else
+    tc_finalize_kernel<__nv_bfloat16><<<fgrid, 256, 0, c.stream>>>(partial, f.splits, p.N, p.r, p.lambda_scale,
+                                                                   (__nv_bfloat16*)delta_out, ds);
+  note_launches(1);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_LAUNCH;
+}
+
+}  // namespace tc
+}  // namespace skv
