@@ -1,0 +1,732 @@
+// tcgen05 backward of the spline-KV feature operator (bf16 I/O).
+//
+// dz kernel (token-major, like the forward):
+//   S[n, (j,m)] = sum_c g[n,c] * T[j,m,c]   on the tensor cores (M = 128 tokens, N = 8L, K = r)
+//   where T is the code table transformed along the knot axis so that the three-of-L selection
+//   becomes a dense weighted sum with one saturating add per column:
+//       T[j,0]   = C[j,1] - C[j,0]
+//       T[j,m+1] = C[j,m] - 2 C[j,m+1] + C[j,m+2]      (m = 0..G-1),   T[j,L-1] = 0
+//       dz_spline[n,j] = scale * 1[0 <= u <= G-1] * ( S[n,(j,0)] + sum_m sat(u_c - m) * S[n,(j,m+1)] )
+//   (sat(u_c - m) is 1 below the token's knot interval, tau inside it and 0 above, which telescopes
+//   to -(1-tau) C[bin] + (1-2tau) C[bin+1] + tau C[bin+2], the B-spline derivative weights.)
+//   One thread per token reads its S row from tensor memory, adds the base-path term
+//   g_a * phi'(z) and stores dz in bf16.
+//
+// dC kernel (key-major):
+//   dC[(j,b), c] = sum_n Phi[n,(j,b)] * g[n,c]  (M = knot rows of a key chunk, N = r, K = tokens)
+//   A CTA owns a slab of keys, keeps the slab's accumulators in tensor memory and streams
+//   128-token tiles: two producer groups alternate, each building the f16 Phi tile of its token
+//   tile for one key chunk in its own shared-memory stage while the MMAs of the other run.
+//   The token range is split over CTAs; a reduce kernel sums the splits in a fixed order.
+//
+// The upstream gradient is converted once per call to f16, multiplied by a power of two chosen
+// from its largest magnitude so that small gradients do not underflow; the inverse factor is
+// applied to the float32 results.
+#include "skv_tc_common.cuh"
+
+namespace skv {
+namespace tc {
+
+size_t cimg_bytes(const skv_problem& p);
+bool fwd_eligible(const skv_problem& p);
+
+namespace {
+
+constexpr int kChunkKeys = 8;
+constexpr int kPlanSMs = 148;
+constexpr size_t kSmemMax = 227 * 1024;
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Power-of-two scale from the bit pattern of max|g|: max|g| * scale lies in [2^12, 2^13).
+__device__ __forceinline__ void g_scales(uint32_t amax_bits, float& scale, float& inv) {
+  const int e = (int)((amax_bits >> 23) & 0xff);
+  if (e == 0 || e == 255) { scale = 1.0f; inv = 1.0f; return; }
+  int se = 127 + 12 - (e - 127);           // biased exponent of 2^(12 - (e-127))
+  se = se < 1 ? 1 : (se > 254 ? 254 : se);
+  scale = __uint_as_float((uint32_t)se << 23);
+  inv = __uint_as_float((uint32_t)(254 - se) << 23);
+}
+
+__global__ void tc_amax_kernel(const __nv_bfloat16* __restrict__ g, int64_t gds, int64_t N, int r,
+                               uint32_t* __restrict__ amax_bits) {
+  const int64_t total = N * r;
+  uint32_t m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = fabsf(__bfloat162float(g[(i / r) * gds + (i % r)]));
+    if (v == v) m = max(m, __float_as_uint(v));
+  }
+  for (int s = 16; s >= 1; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(amax_bits, m);
+}
+
+// g [N][r] bf16 -> scaled f16 image, per 128-token tile the 8x8 core matrices (token rows of 16
+// bytes) at ((cg * 16 + tg) * 128) bytes; rows past N are zero.
+__global__ void tc_pack_g_kernel(const __nv_bfloat16* __restrict__ g, int64_t gds, int64_t N, int r, int64_t tiles,
+                                 const uint32_t* __restrict__ amax_bits, __half* __restrict__ img) {
+  float scale, inv;
+  g_scales(*amax_bits, scale, inv);
+  const int cgs = r / 8;
+  const int64_t pieces = tiles * 128 * cgs;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (int64_t)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % cgs);
+    const int64_t n = i / cgs;
+    uint32_t o[4] = {0, 0, 0, 0};
+    if (n < N) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(g + n * gds + cg * 8));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o[q] = pack_h2(bf_lo(w[q]) * scale, bf_hi(w[q]) * scale);
+    }
+    const int64_t tile = n >> 7;
+    const int t = (int)(n & 127);
+    __half* dst = img + (size_t)tile * 128 * r + ((size_t)cg * 16 + (t >> 3)) * 64 + (t & 7) * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// Transformed table T (see the file header) as an f16 image in the same layout as the forward's
+// code-table image: per 8-key chunk the [8L x r] tile as 8x8 core matrices, core (rowg, cg) at
+// ((rowg * r/8 + cg) * 128) bytes.
+__global__ void tc_pack_t_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int r) {
+  const int rows_per_chunk = kChunkKeys * L;
+  const int cgs = r / 8;
+  const size_t pieces = (size_t)h * L * cgs;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (size_t)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % cgs);
+    const size_t rowg = i / cgs;
+    const int j = (int)(rowg / L), m = (int)(rowg % L);
+    const __nv_bfloat16* base = C + (size_t)j * L * r + cg * 8;
+    float v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (m == 0) v[q] = __bfloat162float(base[r + q]) - __bfloat162float(base[q]);
+      else if (m == L - 1) v[q] = 0.0f;
+      else
+        v[q] = __bfloat162float(base[(size_t)(m - 1) * r + q]) - 2.0f * __bfloat162float(base[(size_t)m * r + q]) +
+               __bfloat162float(base[(size_t)(m + 1) * r + q]);
+    }
+    const int chunk = (int)(rowg / rows_per_chunk);
+    const int k = (int)(rowg % rows_per_chunk);
+    __half* dst = img + (size_t)chunk * rows_per_chunk * r + ((size_t)(k >> 3) * cgs + cg) * 64 + (k & 7) * 8;
+    *reinterpret_cast<uint4*>(dst) =
+        make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+  }
+}
+
+// =================================================================================================
+// dz
+// =================================================================================================
+struct DzParams {
+  const __nv_bfloat16* z;
+  int64_t zs;
+  const __nv_bfloat16* g_act;
+  int64_t gas;
+  __nv_bfloat16* dz;
+  int64_t dzs;
+  const __half* gimg;
+  const __half* timg;
+  const uint32_t* amax_bits;
+  int64_t N;
+  int h, L, r;
+  GridParams g;
+  int act;
+  float coef;                // lambda * scale
+  int chunks_total, chunks_per_split;
+  int32_t* status;
+};
+
+// 8 consecutive float32 columns of this warp's lanes; load and wait in one statement so that no
+// use of the registers can be scheduled before the wait.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+  uint32_t r[8];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int GROUPS, int LB>
+__global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int L = P.L, r = P.r;
+  const uint32_t g_bytes = (uint32_t)(128 * r * 2);
+  const uint32_t t_bytes = (uint32_t)(kChunkKeys * L * r * 2);
+  const uint32_t ncols = (uint32_t)(kChunkKeys * L);               // S columns per group
+  uint8_t* g_base = smem;                                           // [group][g_bytes]
+  uint8_t* t_base = smem + (size_t)GROUPS * g_bytes;                // [2][t_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(t_base + 2 * (size_t)t_bytes);
+  uint64_t* gfull = bars;               // [1]
+  uint64_t* tfull = gfull + 1;          // [2]
+  uint64_t* tempty = tfull + 2;         // [2]
+  uint64_t* sfull = tempty + 2;         // [GROUPS]
+  uint64_t* sempty = sfull + GROUPS;    // [GROUPS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty + GROUPS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunk_begin = blockIdx.y * P.chunks_per_split;
+  const int nch = min(P.chunks_per_split, P.chunks_total - chunk_begin);
+  const int64_t tile_base = (int64_t)blockIdx.x * (128 * GROUPS);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < GROUPS * ncols + 8) tmem_cols <<= 1;           // +8: the last 8-column load may overhang
+
+  if (tid == 0) {
+    mbar_init(gfull, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 1); }
+    for (int i = 0; i < GROUPS; ++i) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 128); }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 4 * GROUPS) tmem_alloc(tmem_slot, tmem_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4 * GROUPS) {
+    // ------------------------------------------------------------------ one thread per token
+    const int grp = warp >> 2;
+    const int t = tid & 127;
+    const int64_t n = tile_base + grp * 128 + t;
+    const bool valid = n < P.N;
+    const int64_t nn = valid ? n : 0;
+    const __nv_bfloat16* zrow = P.z + nn * P.zs + (int64_t)chunk_begin * kChunkKeys;
+    const __nv_bfloat16* garow = P.g_act ? P.g_act + nn * P.gas + (int64_t)chunk_begin * kChunkKeys : nullptr;
+    __nv_bfloat16* dzrow = P.dz + nn * P.dzs + (int64_t)chunk_begin * kChunkKeys;
+    float gscale, ginv;
+    g_scales(*P.amax_bits, gscale, ginv);
+    const float coef = P.coef * ginv;
+    const int Lm1 = L - 1;
+    const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * ncols;
+    uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
+    uint4 ganext = valid && nch > 0 && garow ? __ldg(reinterpret_cast<const uint4*>(garow)) : make_uint4(0, 0, 0, 0);
+
+    for (int ci = 0; ci < nch; ++ci) {
+      const uint4 zc = znext, gac = ganext;
+      if (ci + 1 < nch && valid) {
+        znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
+        if (garow) ganext = __ldg(reinterpret_cast<const uint4*>(garow + (ci + 1) * kChunkKeys));
+      }
+      mbar_wait(sfull + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutDz);
+      tc_fence_after();
+      const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
+      const uint32_t gw[4] = {gac.x, gac.y, gac.z, gac.w};
+      float outv[kChunkKeys];
+#pragma unroll
+      for (int q = 0; q < kChunkKeys; ++q) {
+        const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+        const float u = __fmul_rn(__fsub_rn(zz, P.g.lo), P.g.scale);
+        const bool active = (u >= 0.0f) && (u <= P.g.Gm1f);
+        const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
+        float acc = 0.0f;
+#pragma unroll
+        for (int blk = 0; blk < LB; ++blk) {
+          float v[8];
+          tmem_ld8(trow + (uint32_t)(q * L + blk * 8), v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = blk * 8 + i;           // column of this key: 0 = constant term, m>=1: T[m-1]
+            if (m == 0) acc = v[0];
+            else if (m < Lm1) acc = fmaf(__saturatef(uc - (float)(m - 1)), v[i], acc);
+          }
+        }
+        float o = active ? coef * acc : 0.0f;
+        if (garow) {
+          const float ga = (q & 1) ? bf_hi(gw[q >> 1]) : bf_lo(gw[q >> 1]);
+          o = fmaf(ga, act_grad(zz, P.act), o);
+        }
+        outv[q] = o;
+      }
+      tc_fence_before();
+      mbar_arrive(sempty + grp);
+      if (valid)
+        *reinterpret_cast<uint4*>(dzrow + ci * kChunkKeys) =
+            make_uint4(pack_bf2(outv[0], outv[1]), pack_bf2(outv[2], outv[3]), pack_bf2(outv[4], outv[5]),
+                       pack_bf2(outv[6], outv[7]));
+    }
+  } else if (warp == 4 * GROUPS) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      mbar_wait(gfull, 0, abort_flag, P.status, kStatusTimeoutDz);
+      const uint32_t rb = (uint32_t)(r / 8) * 128u;          // bytes between 8-row groups of the T image
+      for (int ci = 0; ci < nch; ++ci) {
+        const int s = ci & 1;
+        mbar_wait(tfull + s, (uint32_t)(ci >> 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        const uint32_t b_addr = smem_u32(t_base + (size_t)s * t_bytes);
+        for (int grp = 0; grp < GROUPS; ++grp) {
+          if (ci > 0) mbar_wait(sempty + grp, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(g_base + (size_t)grp * g_bytes);
+          for (uint32_t c0 = 0; c0 < ncols; c0 += 256) {
+            const uint32_t npiece = min(256u, ncols - c0);
+            const uint32_t idesc = instr_desc(0, 0, 0, 0, 128, (int)npiece);
+            for (int ks = 0; ks < r / 16; ++ks) {
+              const uint64_t ad = smem_desc(a_addr + (uint32_t)ks * 4096u, 2048u, 128u);
+              const uint64_t bd = smem_desc(b_addr + (c0 / 8) * rb + (uint32_t)ks * 256u, 128u, rb);
+              umma_f16(tmem_base + (uint32_t)grp * ncols + c0, ad, bd, idesc, ks > 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(sfull + grp);
+        }
+        umma_commit(tempty + s);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      mbar_arrive_expect_tx(gfull, GROUPS * g_bytes);
+      for (int grp = 0; grp < GROUPS; ++grp)
+        bulk_g2s(g_base + (size_t)grp * g_bytes,
+                 reinterpret_cast<const uint8_t*>(P.gimg) + (size_t)(blockIdx.x * GROUPS + grp) * g_bytes, g_bytes,
+                 gfull);
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(P.timg) + (size_t)chunk_begin * t_bytes;
+      for (int ci = 0; ci < nch; ++ci) {
+        const int s = ci & 1;
+        if (ci >= 2) mbar_wait(tempty + s, (uint32_t)((ci >> 1) - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(tfull + s, t_bytes);
+        bulk_g2s(t_base + (size_t)s * t_bytes, src + (size_t)ci * t_bytes, t_bytes, tfull + s);
+      }
+      if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4 * GROUPS) {
+    tc_fence_after();
+    tmem_free(tmem_base, tmem_cols);
+  }
+}
+
+// =================================================================================================
+// dC
+// =================================================================================================
+struct DcParams {
+  const __nv_bfloat16* z;
+  int64_t zs;
+  const __half* gimg;
+  float* part;               // [splits][h*L][r]
+  int64_t N;
+  int h, L, r;
+  GridParams g;
+  int kch;                   // keys per chunk (8 or 16)
+  int mtiles;                // 128-row MMA tiles per chunk
+  int slab_chunks;           // chunks per CTA slab
+  int64_t tiles_per_split;   // 128-token tiles per token split
+  int64_t tiles_total;
+  int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t word_off(uint32_t w) { return (w >> 2) * 2048u + (w & 3u) * 4u; }
+
+// KCH = keys per chunk.  Two producer groups of 128 threads (thread = token of the group's tile).
+template <int KCH>
+__global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int L = P.L, r = P.r;
+  const uint32_t phi_bytes = (uint32_t)P.mtiles * 16u * 2048u;     // [m groups][16 token groups][8 tok][8 m]
+  const uint32_t g_bytes = (uint32_t)(128 * r * 2);
+  uint8_t* phi_base = smem;                                         // [2][phi_bytes]
+  uint8_t* g_base = smem + 2 * (size_t)phi_bytes;                   // [2][g_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(g_base + 2 * (size_t)g_bytes);
+  uint64_t* pfull = bars;          // [2] producers -> MMA
+  uint64_t* pempty = pfull + 2;    // [2] MMA -> producers
+  uint64_t* gfull = pempty + 2;    // [2] TMA -> MMA
+  uint64_t* gempty = gfull + 2;    // [2] MMA -> TMA
+  uint64_t* done = gempty + 2;     // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rows = KCH * L;                                          // knot rows per chunk
+  const int key0 = blockIdx.x * P.slab_chunks * KCH;
+  const int nchunks = min(P.slab_chunks, (P.h - key0 + KCH - 1) / KCH);
+  const int64_t tile_begin = (int64_t)blockIdx.y * P.tiles_per_split;
+  const int ntiles = (int)min(P.tiles_per_split, P.tiles_total - tile_begin);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < (uint32_t)(P.slab_chunks * P.mtiles * r)) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(pfull + i, 128);
+      mbar_init(pempty + i, 1);
+      mbar_init(gfull + i, 1);
+      mbar_init(gempty + i, 1);
+    }
+    mbar_init(done, 1);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  {
+    uint4* p = reinterpret_cast<uint4*>(phi_base);
+    const uint32_t n16 = 2 * phi_bytes / 16;
+    for (uint32_t i = tid; i < n16; i += blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (warp == 8) tmem_alloc(tmem_slot, tmem_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ producers
+    const int pg = warp >> 2;
+    const int t = tid & 127;
+    const uint32_t t_off = (uint32_t)(t & 7) * 16u + (uint32_t)(t >> 3) * 128u;
+    const uint32_t row = smem_u32(phi_base + (size_t)pg * phi_bytes) + t_off;
+    const uint32_t halfL = (uint32_t)L >> 1;
+    uint32_t saved[KCH / 4];
+#pragma unroll
+    for (int i = 0; i < KCH / 4; ++i) saved[i] = 0;
+    bool have_saved = false;
+    int use = 0;                                     // how often this group's stage has been filled
+    for (int ti = pg; ti < ntiles; ti += 2) {
+      const int64_t n = (tile_begin + ti) * 128 + t;
+      const bool valid = n < P.N;
+      const __nv_bfloat16* zrow = P.z + (valid ? n : 0) * P.zs + key0;
+      for (int ch = 0; ch < nchunks; ++ch, ++use) {
+        uint4 zq[KCH / 8];
+#pragma unroll
+        for (int i = 0; i < KCH / 8; ++i) {
+          const bool in_h = key0 + ch * KCH + i * 8 < P.h;
+          zq[i] = valid && in_h ? __ldg(reinterpret_cast<const uint4*>(zrow + ch * KCH + i * 8)) : make_uint4(0, 0, 0, 0);
+        }
+        if (use > 0) mbar_wait(pempty + pg, (uint32_t)(use - 1) & 1u, abort_flag, P.status, kStatusTimeoutDc);
+        if (have_saved) {
+#pragma unroll
+          for (int q = 0; q < KCH; ++q) {
+            const uint32_t w0 = (saved[q >> 2] >> ((q & 3) * 8)) & 0xffu;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(0u) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(0u) : "memory");
+          }
+          have_saved = false;
+        }
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < KCH / 4; ++i) saved[i] = 0;
+#pragma unroll
+          for (int q = 0; q < KCH; ++q) {
+            const uint4& zc = zq[q >> 3];
+            const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
+            const int qq = q & 7;
+            const float zz = (qq & 1) ? bf_hi(zw[qq >> 1]) : bf_lo(zw[qq >> 1]);
+            const bool in_h = key0 + ch * KCH + q < P.h;
+            const Knot k = knot_of(zz, P.g);
+            float B0, B1, B2;
+            basis_weights(k, B0, B1, B2);
+            if (!in_h) { B0 = 0.f; B1 = 0.f; B2 = 0.f; }
+            const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
+            const bool odd = (k.bin & 1) != 0;
+            const uint32_t x0 = odd ? (p01 << 16) : p01;
+            const uint32_t x1 = odd ? __funnelshift_r(p01, p2, 16) : p2;
+            const uint32_t w0 = (uint32_t)q * halfL + ((uint32_t)k.bin >> 1);
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(x0) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(x1) : "memory");
+            saved[q >> 2] |= w0 << ((q & 3) * 8);
+          }
+          have_saved = true;
+        }
+        fence_async_smem();
+        mbar_arrive(pfull + pg);
+      }
+    }
+    // ---- epilogue: accumulators -> float32 partial of this token split
+    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutDc);
+    tc_fence_after();
+    const int lane_row = (warp & 3) * 32 + lane;
+    float* part = P.part + (size_t)blockIdx.y * P.h * L * r;
+    for (int ch = pg; ch < nchunks; ch += 2) {
+      for (int mt = 0; mt < P.mtiles; ++mt) {
+        const int rr = mt * 128 + lane_row;                        // knot row within the chunk
+        const int key = key0 + ch * KCH + rr / L;
+        const bool ok = rr < rows && key < P.h;
+        float* dst = part + ((size_t)(key0 + ch * KCH) * L + rr) * r;
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((ch * P.mtiles + mt) * r);
+        for (int c0 = 0; c0 < r; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          if (ok) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4*>(dst + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(0, 0, 1, 1, 128, r);
+      int guse[2] = {0, 0}, puse[2] = {0, 0};
+      for (int tp = 0; tp < ntiles; tp += 2) {
+        const int npg = min(2, ntiles - tp);
+        for (int pg = 0; pg < npg; ++pg)
+          mbar_wait(gfull + pg, (uint32_t)guse[pg] & 1u, abort_flag, P.status, kStatusTimeoutDc);
+        for (int ch = 0; ch < nchunks; ++ch) {
+          for (int pg = 0; pg < npg; ++pg) {
+            mbar_wait(pfull + pg, (uint32_t)puse[pg] & 1u, abort_flag, P.status, kStatusTimeoutDc);
+            ++puse[pg];
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(phi_base + (size_t)pg * phi_bytes);
+            const uint32_t b_addr = smem_u32(g_base + (size_t)pg * g_bytes);
+            const uint32_t first = (tp == 0 && pg == 0) ? 0u : 1u;
+            for (int mt = 0; mt < P.mtiles; ++mt) {
+              for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t ad = smem_desc(a_addr + (uint32_t)mt * 16u * 2048u + (uint32_t)ks * 256u, 128u, 2048u);
+                const uint64_t bd = smem_desc(b_addr + (uint32_t)ks * 256u, 128u, 2048u);
+                umma_f16(tmem_base + (uint32_t)((ch * P.mtiles + mt) * r), ad, bd, idesc, (first | (ks > 0)) ? 1u : 0u);
+              }
+            }
+            umma_commit(pempty + pg);
+          }
+        }
+        for (int pg = 0; pg < npg; ++pg) { umma_commit(gempty + pg); ++guse[pg]; }
+      }
+      umma_commit(done);
+    }
+  } else {
+    // ------------------------------------------------------------------ gradient-tile loader
+    if (lane == 0) {
+      int guse[2] = {0, 0};
+      for (int ti = 0; ti < ntiles; ++ti) {
+        const int pg = ti & 1;
+        if (guse[pg] > 0)
+          mbar_wait(gempty + pg, (uint32_t)(guse[pg] - 1) & 1u, abort_flag, P.status, kStatusTimeoutDc);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(gfull + pg, g_bytes);
+        bulk_g2s(g_base + (size_t)pg * g_bytes,
+                 reinterpret_cast<const uint8_t*>(P.gimg) + (size_t)(tile_begin + ti) * g_bytes, g_bytes, gfull + pg);
+        ++guse[pg];
+      }
+      if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 8) {
+    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutDc);
+    tc_fence_after();
+    tmem_free(tmem_base, tmem_cols);
+  }
+}
+
+__global__ void tc_dc_reduce_kernel(const float* __restrict__ part, int splits, size_t elems, float lambda,
+                                    const uint32_t* __restrict__ amax_bits, float* __restrict__ dC,
+                                    __nv_bfloat16* __restrict__ dC_cast) {
+  float gscale, ginv;
+  g_scales(*amax_bits, gscale, ginv);
+  const float f = lambda * ginv;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (size_t)gridDim.x * blockDim.x) {
+    float s = 0.0f;
+    for (int k = 0; k < splits; ++k) s += part[(size_t)k * elems + i];
+    s *= f;
+    if (dC) dC[i] = s;
+    if (dC_cast) dC_cast[i] = __float2bfloat16_rn(s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+struct DzPlan { int groups, lb, splits, chunks_per_split; size_t smem; };
+
+bool plan_dz(const skv_problem& p, DzPlan* o) {
+  const int ncols = kChunkKeys * p.L;
+  int groups = 2 * ncols + 8 <= 512 ? 2 : (ncols + 8 <= 512 ? 1 : 0);
+  if (!groups) return false;
+  const int lb = (p.L - 1 + 7) / 8;
+  if (lb < 1 || lb > 6 || (groups == 2 && lb > 4) || (groups == 1 && lb < 4)) return false;
+  o->groups = groups;
+  o->lb = lb;
+  o->smem = (size_t)groups * 128 * p.r * 2 + 2 * (size_t)kChunkKeys * p.L * p.r * 2 + 256;
+  if (o->smem > kSmemMax) return false;
+  const int chunks = p.h / kChunkKeys;
+  const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
+  int best = 1;
+  double best_eff = 0.0;
+  const int max_splits = chunks >= 16 ? (chunks / 8 < 16 ? chunks / 8 : 16) : 1;
+  for (int ks = 1; ks <= max_splits; ++ks) {
+    const double waves = (double)(tiles > 0 ? tiles : 1) * ks / kPlanSMs;
+    const double eff = waves / (double)(int64_t)(waves + 0.999999);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = ks; }
+  }
+  o->chunks_per_split = (chunks + best - 1) / best;
+  o->splits = (chunks + o->chunks_per_split - 1) / o->chunks_per_split;
+  return true;
+}
+
+struct DcPlan { int kch, mtiles, slab_chunks, slabs, splits; int64_t tiles_total, tiles_per_split; size_t smem; };
+
+bool plan_dc(const skv_problem& p, DcPlan* o) {
+  for (int kch = 16; kch >= 8; kch /= 2) {
+    const int rows = kch * p.L;
+    const int mtiles = (rows + 127) / 128;
+    if (mtiles > 3) continue;
+    const size_t smem = 2 * (size_t)mtiles * 16 * 2048 + 2 * (size_t)128 * p.r * 2 + 256;
+    if (smem > kSmemMax) continue;
+    int slab_chunks = 512 / (mtiles * p.r);
+    if (slab_chunks < 1) continue;
+    if (slab_chunks > 8) slab_chunks = 8;
+    const int chunks = (p.h + kch - 1) / kch;
+    if (slab_chunks > chunks) slab_chunks = chunks;
+    o->kch = kch;
+    o->mtiles = mtiles;
+    o->slab_chunks = slab_chunks;
+    o->slabs = (chunks + slab_chunks - 1) / slab_chunks;
+    o->smem = smem;
+    o->tiles_total = (p.N + 127) / 128;
+    const int64_t tt = o->tiles_total > 0 ? o->tiles_total : 1;
+    int best = 1;
+    double best_eff = 0.0;
+    const int64_t max_splits = tt / 4 < 1 ? 1 : (tt / 4 > 32 ? 32 : tt / 4);
+    for (int ns = 1; ns <= max_splits; ++ns) {
+      const double waves = (double)o->slabs * ns / kPlanSMs;
+      const double eff = waves / (double)(int64_t)(waves + 0.999999);
+      if (eff > best_eff + 0.02) { best_eff = eff; best = ns; }
+    }
+    o->tiles_per_split = (tt + best - 1) / best;
+    o->splits = (int)((tt + o->tiles_per_split - 1) / o->tiles_per_split);
+    return true;
+  }
+  return false;
+}
+
+size_t gimg_bytes(const skv_problem& p) {
+  const int64_t tiles = ((p.N + 255) / 256) * 2;
+  return align256((size_t)(tiles > 0 ? tiles : 2) * 128 * p.r * 2);
+}
+
+}  // namespace
+
+bool bwd_eligible(const skv_problem& p) {
+  if (!fwd_eligible(p)) return false;
+  DzPlan a;
+  DcPlan b;
+  return plan_dz(p, &a) && plan_dc(p, &b);
+}
+
+size_t bwd_scratch_bytes(const skv_problem& p) {
+  DcPlan d;
+  if (!plan_dc(p, &d)) return 0;
+  return 256 + gimg_bytes(p) + cimg_bytes(p) + align256((size_t)d.splits * p.h * p.L * p.r * sizeof(float));
+}
+
+int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const void* g_act, int64_t gas,
+             const void* g_delta, int64_t gds, void* dz, int64_t dzs, float* dC, void* dC_cast, void* scratch,
+             size_t scratch_bytes) {
+  const skv_problem& p = c.p;
+  DzPlan zp;
+  DcPlan dp;
+  if (!plan_dz(p, &zp) || !plan_dc(p, &dp)) return SKV_ERR_UNSUPPORTED;
+  if (scratch_bytes < bwd_scratch_bytes(p)) return SKV_ERR_SCRATCH;
+  uint8_t* base = reinterpret_cast<uint8_t*>(scratch);
+  uint32_t* amax = reinterpret_cast<uint32_t*>(base);
+  __half* gimg = reinterpret_cast<__half*>(base + 256);
+  __half* timg = reinterpret_cast<__half*>(base + 256 + gimg_bytes(p));
+  float* part = reinterpret_cast<float*>(base + 256 + gimg_bytes(p) + cimg_bytes(p));
+
+  if (cudaMemsetAsync(amax, 0, 256, c.stream) != cudaSuccess) return SKV_ERR_LAUNCH;
+  {
+    const int64_t total = p.N * p.r;
+    const unsigned grid = (unsigned)((total + 1023) / 1024 < 1184 ? (total + 1023) / 1024 : 1184);
+    tc_amax_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)g_delta, gds, p.N, p.r, amax);
+    const int64_t tiles = ((p.N + 255) / 256) * 2;
+    const int64_t pieces = tiles * 128 * (p.r / 8);
+    const unsigned pgrid = (unsigned)((pieces + 255) / 256 < 2368 ? (pieces + 255) / 256 : 2368);
+    tc_pack_g_kernel<<<pgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)g_delta, gds, p.N, p.r, tiles, amax, gimg);
+    note_launches(2);
+    if (cudaGetLastError() != cudaSuccess) return SKV_ERR_LAUNCH;
+  }
+
+  if (dz) {
+    const size_t pieces = (size_t)p.h * p.L * (p.r / 8);
+    const unsigned tgrid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
+    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, p.r);
+    note_launches(1);
+    DzParams P;
+    P.z = (const __nv_bfloat16*)z;
+    P.zs = zs;
+    P.g_act = (const __nv_bfloat16*)g_act;
+    P.gas = gas;
+    P.dz = (__nv_bfloat16*)dz;
+    P.dzs = dzs;
+    P.gimg = gimg;
+    P.timg = timg;
+    P.amax_bits = amax;
+    P.N = p.N;
+    P.h = p.h;
+    P.L = p.L;
+    P.r = p.r;
+    P.g = c.g;
+    P.act = p.activation;
+    P.coef = p.lambda_scale * c.g.scale;
+    P.chunks_total = p.h / kChunkKeys;
+    P.chunks_per_split = zp.chunks_per_split;
+    P.status = c.status;
+    const int64_t tiles = (p.N + 128 * zp.groups - 1) / (128 * zp.groups);
+    dim3 grid((unsigned)tiles, (unsigned)zp.splits);
+    const unsigned threads = 128 * zp.groups + 64;
+    cudaError_t err = cudaErrorInvalidValue;
+#define SKV_DZ_CASE(G_, LB_)                                                                                      \
+  if (zp.groups == G_ && zp.lb == LB_) {                                                                          \
+    err = cudaFuncSetAttribute(tc_dz_kernel<G_, LB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)zp.smem); \
+    if (err == cudaSuccess) tc_dz_kernel<G_, LB_><<<grid, threads, zp.smem, c.stream>>>(P);                       \
+  }
+    SKV_DZ_CASE(2, 1) SKV_DZ_CASE(2, 2) SKV_DZ_CASE(2, 3) SKV_DZ_CASE(2, 4)
+    SKV_DZ_CASE(1, 4) SKV_DZ_CASE(1, 5) SKV_DZ_CASE(1, 6)
+#undef SKV_DZ_CASE
+    note_launches(1);
+    if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }
+  }
+
+  if (dC || dC_cast) {
+    DcParams P;
+    P.z = (const __nv_bfloat16*)z;
+    P.zs = zs;
+    P.gimg = gimg;
+    P.part = part;
+    P.N = p.N;
+    P.h = p.h;
+    P.L = p.L;
+    P.r = p.r;
+    P.g = c.g;
+    P.kch = dp.kch;
+    P.mtiles = dp.mtiles;
+    P.slab_chunks = dp.slab_chunks;
+    P.tiles_per_split = dp.tiles_per_split;
+    P.tiles_total = dp.tiles_total;
+    P.status = c.status;
+    dim3 grid((unsigned)dp.slabs, (unsigned)dp.splits);
+    cudaError_t err;
+    if (dp.kch == 16) {
+      err = cudaFuncSetAttribute(tc_dc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
+      if (err == cudaSuccess) tc_dc_kernel<16><<<grid, 320, dp.smem, c.stream>>>(P);
+    } else {
+      err = cudaFuncSetAttribute(tc_dc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
+      if (err == cudaSuccess) tc_dc_kernel<8><<<grid, 320, dp.smem, c.stream>>>(P);
+    }
+    note_launches(1);
+    if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }
+    const size_t elems = (size_t)p.h * p.L * p.r;
+    const unsigned rgrid = (unsigned)((elems + 255) / 256 < 4096 ? (elems + 255) / 256 : 4096);
+    tc_dc_reduce_kernel<<<rgrid, 256, 0, c.stream>>>(part, dp.splits, elems, p.lambda_scale, amax, dC,
+                                                     (__nv_bfloat16*)dC_cast);
+    note_launches(1);
+    if (cudaGetLastError() != cudaSuccess) return SKV_ERR_LAUNCH;
+  }
+  return SKV_OK;
+}
+
+}  // namespace tc
+}  // namespace skv
