@@ -270,7 +270,10 @@ def main():
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         with open(tpath) as f:
-            traffic = json.load(f).get(f"{impl}:{dominant}")
+            rec = json.load(f).get(f"{impl}:{dominant}")
+        if rec:
+            # captured at a reduced token count; the large streams are per-token, so it scales with N
+            traffic = rec["bytes_per_launch_65536_tokens"] * N / 65536
     roofline = dict(bound="tensor", kernel=f"{impl}:{dominant}", achieved=achieved, peak=peaks["bf16_tflops"],
                     unit="TFLOP/s", frac=achieved / peaks["bf16_tflops"], traffic=traffic,
                     peak_source=peaks["source"] + " burst bf16 (kernel timed alone)",
