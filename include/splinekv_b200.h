@@ -34,7 +34,8 @@ enum skv_error {
   SKV_ERR_ALIGN = -4,       /* pointer or stride alignment the chosen kernel needs is not met */
   SKV_ERR_SCRATCH = -5,     /* scratch buffer missing or smaller than skv_scratch_bytes() */
   SKV_ERR_DEVICE = -6,      /* current device is not compute capability 10.x */
-  SKV_ERR_LAUNCH = -7       /* a kernel launch failed (cudaGetLastError) */
+  SKV_ERR_LAUNCH = -7,      /* a kernel launch failed (cudaGetLastError) */
+  SKV_ERR_NOALLOC_LIMIT = -8 /* problem needs more than SKV_NOALLOC_SCRATCH_BYTES of scratch */
 };
 
 enum skv_dtype { SKV_BF16 = 0, SKV_F32 = 1 };
@@ -118,6 +119,29 @@ int skv_feature_backward(const skv_problem *p, const void *z, int64_t z_stride, 
  * function all kernels use.  Lets a caller check indices bit for bit against
  * _b2_basis_and_bins (src/sparsespline_ffn/rl_spline_kv_reference.py:88-109). */
 int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_t *bins, void *stream);
+
+/* Forward for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * kernels allocate their scratch themselves through the PyTorch allocator).  Same arguments and
+ * results as skv_feature_forward minus the scratch pair: the scratch is a fixed array of
+ * SKV_NOALLOC_SCRATCH_BYTES inside the library's device image, which every GPU that loads the
+ * library holds until the process exits.  It exists for hosts where cudaMalloc is not an option
+ * when the operator runs: inside CUDA-graph capture, in servers and plugin sandboxes that fix
+ * their device memory at start-up, in latency-critical loops.  This call itself uses no
+ * cudaMalloc, cudaFree or allocating library routine.
+ *  - A problem whose skv_scratch_bytes(p, SKV_OP_FORWARD) exceeds the array is refused with
+ *    SKV_ERR_NOALLOC_LIMIT (at h = 5120, L = 22, r = 32, N = 8192 tokens fit and N = 16384
+ *    do not; use skv_feature_forward with caller-owned scratch beyond the limit).
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call before any stream
+ *    capture begins.
+ *  - All calls on a device share the one array.  Its contents are whatever the previous call
+ *    left; the forward overwrites everything it reads, so nothing needs clearing, but two calls
+ *    whose kernels overlap on the GPU (different streams, or graphs replayed concurrently)
+ *    race on it.  Serialise them. */
+#define SKV_NOALLOC_SCRATCH_BYTES (16u << 20)
+int skv_feature_forward_noalloc(const skv_problem *p, const void *z, int64_t z_stride, const void *C,
+                                void *act_out, int64_t act_stride, void *delta_out, int64_t delta_stride,
+                                int32_t *status, void *stream);
 
 /* Number of kernels this library has launched in this process so far (host-side counter).  No
  * counterpart in the reference; benchmarks use the difference around a timed region to report

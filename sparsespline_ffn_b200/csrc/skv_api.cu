@@ -93,6 +93,9 @@ const char* skv_error_string(int code) {
     case SKV_ERR_SCRATCH: return "scratch buffer missing or smaller than skv_scratch_bytes()";
     case SKV_ERR_DEVICE: return "current CUDA device is not compute capability 10.x (B200, sm_100a)";
     case SKV_ERR_LAUNCH: return "CUDA kernel launch failed";
+    case SKV_ERR_NOALLOC_LIMIT:
+      return "problem needs more scratch than the built-in SKV_NOALLOC_SCRATCH_BYTES array; use "
+             "skv_feature_forward with caller-owned scratch";
     default: return "unknown error code";
   }
 }
