@@ -125,9 +125,10 @@ int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_
  * results as skv_feature_forward minus the scratch pair: the scratch is a fixed array of
  * SKV_NOALLOC_SCRATCH_BYTES inside the library's device image, which every GPU that loads the
  * library holds until the process exits.  It exists for hosts where cudaMalloc is not an option
- * when the operator runs: inside CUDA-graph capture, in servers and plugin sandboxes that fix
- * their device memory at start-up, in latency-critical loops.  This call itself uses no
- * cudaMalloc, cudaFree or allocating library routine.
+ * when the operator runs: servers and plugin sandboxes that fix their device memory at
+ * start-up, and latency-critical loops that cannot afford an allocation's cost and implicit
+ * synchronisation.  This call itself uses no cudaMalloc, cudaFree or allocating library
+ * routine.  (Nothing is stated here about recording it into a CUDA graph.)
  *  - A problem whose skv_scratch_bytes(p, SKV_OP_FORWARD) exceeds the array is refused with
  *    SKV_ERR_NOALLOC_LIMIT (at h = 5120, L = 22, r = 32, N = 8192 tokens fit and N = 16384
  *    do not; use skv_feature_forward with caller-owned scratch beyond the limit).
@@ -136,7 +137,7 @@ int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_
  *    capture begins.
  *  - All calls on a device share the one array.  Its contents are whatever the previous call
  *    left; the forward overwrites everything it reads, so nothing needs clearing, but two calls
- *    whose kernels overlap on the GPU (different streams, or graphs replayed concurrently)
+ *    whose kernels overlap on the GPU (for instance on different streams)
  *    race on it.  Serialise them. */
 #define SKV_NOALLOC_SCRATCH_BYTES (16u << 20)
 int skv_feature_forward_noalloc(const skv_problem *p, const void *z, int64_t z_stride, const void *C,

@@ -1,9 +1,9 @@
 // Forward entry point for callers that must not allocate device memory.
 //
 // Some hosts of this library cannot call cudaMalloc at the point where they run the operator:
-// code executing inside a CUDA-graph capture or a fixed-memory inference server, plugin sandboxes
-// that forbid allocation after start-up, and real-time loops where an allocation's latency and
-// implicit synchronisation are not acceptable.  The regular forward asks such a caller for a
+// inference servers with a fixed device-memory budget, plugin sandboxes that forbid allocation
+// after start-up, and real-time loops where an allocation's latency and implicit synchronisation
+// are not acceptable.  The regular forward asks such a caller for a
 // scratch buffer it has no way to obtain.  This variant brings its own: a fixed array in the
 // library's device image.
 #include <mutex>

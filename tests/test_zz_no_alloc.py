@@ -1,8 +1,7 @@
 """The allocation-free forward entry point, called through the C ABI.
 
 `skv_feature_forward_noalloc` is for hosts that cannot call cudaMalloc where the operator runs
-(CUDA-graph capture, servers and plugin sandboxes with fixed device memory, latency-critical
-loops): it carries its scratch as a fixed array inside the library.  Here it is compared with the
+(servers and plugin sandboxes with a fixed device-memory budget, latency-critical loops): it carries its scratch as a fixed array inside the library.  Here it is compared with the
 regular entry point (caller-owned scratch) on two calls in a row with different inputs, since all
 calls share the one array, and the size limit is checked.  The file is named so that pytest
 collects it last.
