@@ -30,6 +30,10 @@ namespace tc {
 size_t cimg_bytes(const skv_problem& p);
 bool fwd_eligible(const skv_problem& p);
 
+#ifdef SKV_TC_PROFILE
+long long* g_prof_bwd = nullptr;
+#endif
+
 namespace {
 
 constexpr int kChunkKeys = 8;
@@ -85,23 +89,25 @@ __global__ void tc_pack_g_kernel(const __nv_bfloat16* __restrict__ g, int64_t gd
   }
 }
 
-// Transformed table T (see the file header) as an f16 image in the same layout as the forward's
-// code-table image: per 8-key chunk the [8L x r] tile as 8x8 core matrices, core (rowg, cg) at
+// Transformed table T (see the file header) as an f16 image in the same core-matrix layout as the
+// forward's code-table image, with every key padded to LP (a multiple of 8) rows of which rows
+// L-1.. are zero: per 8-key chunk the [8*LP x r] tile as 8x8 core matrices, core (rowg, cg) at
 // ((rowg * r/8 + cg) * 128) bytes.
-__global__ void tc_pack_t_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int r) {
-  const int rows_per_chunk = kChunkKeys * L;
+__global__ void tc_pack_t_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int LP,
+                                 int r) {
+  const int rows_per_chunk = kChunkKeys * LP;
   const int cgs = r / 8;
-  const size_t pieces = (size_t)h * L * cgs;
+  const size_t pieces = (size_t)h * LP * cgs;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (size_t)gridDim.x * blockDim.x) {
     const int cg = (int)(i % cgs);
     const size_t rowg = i / cgs;
-    const int j = (int)(rowg / L), m = (int)(rowg % L);
+    const int j = (int)(rowg / LP), m = (int)(rowg % LP);
     const __nv_bfloat16* base = C + (size_t)j * L * r + cg * 8;
     float v[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       if (m == 0) v[q] = __bfloat162float(base[r + q]) - __bfloat162float(base[q]);
-      else if (m == L - 1) v[q] = 0.0f;
+      else if (m >= L - 1) v[q] = 0.0f;
       else
         v[q] = __bfloat162float(base[(size_t)(m - 1) * r + q]) - 2.0f * __bfloat162float(base[(size_t)m * r + q]) +
                __bfloat162float(base[(size_t)(m + 1) * r + q]);
@@ -134,37 +140,77 @@ struct DzParams {
   float coef;                // lambda * scale
   int chunks_total, chunks_per_split;
   int32_t* status;
+#ifdef SKV_TC_PROFILE
+  long long* prof;
+#endif
 };
 
-// 8 consecutive float32 columns of this warp's lanes; load and wait in one statement so that no
-// use of the registers can be scheduled before the wait.
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
-  uint32_t r[8];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-      : "r"(taddr)
-      : "memory");
+#ifdef SKV_TC_PROFILE
+#define SKV_T(x) const long long x = clock64()
+#define SKV_ACC(a, expr) a += (expr)
+#else
+#define SKV_T(x)
+#define SKV_ACC(a, expr)
+#endif
+
+// Tensor-memory loads of one key's S columns (LB blocks of 8 float32 columns of this warp's lanes).
+// The loads are issued without waiting; tmem_wait_key waits for all outstanding loads and ties
+// the destination registers to the wait so that no use can be scheduled ahead of it.
+template <int LB>
+__device__ __forceinline__ void tmem_ld_key(uint32_t taddr, uint32_t (&r)[LB][8]) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+  for (int blk = 0; blk < LB; ++blk)
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[blk][0]), "=r"(r[blk][1]), "=r"(r[blk][2]), "=r"(r[blk][3]), "=r"(r[blk][4]),
+                   "=r"(r[blk][5]), "=r"(r[blk][6]), "=r"(r[blk][7])
+                 : "r"(taddr + (uint32_t)blk * 8u)
+                 : "memory");
 }
+template <int LB>
+__device__ __forceinline__ void tmem_wait_key(uint32_t (&r)[LB][8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int blk = 0; blk < LB; ++blk)
+    asm volatile("" : "+r"(r[blk][0]), "+r"(r[blk][1]), "+r"(r[blk][2]), "+r"(r[blk][3]), "+r"(r[blk][4]),
+                      "+r"(r[blk][5]), "+r"(r[blk][6]), "+r"(r[blk][7])
+                 :
+                 : "memory");
+}
+
+// S_0 + sum_m sat(uc - m) * S_{m+1} over the 8*LB columns of one key (padding columns are zero in
+// the table image and their weight sat(uc - m) is zero as well, since uc <= G-1 < m).
+template <int LB>
+__device__ __forceinline__ float dz_key_sum(const uint32_t (&r)[LB][8], float uc) {
+  float acc = __uint_as_float(r[0][0]);
+#pragma unroll
+  for (int blk = 0; blk < LB; ++blk) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int m = blk * 8 + i;
+      if (m > 0) acc = fmaf(__saturatef(uc - (float)(m - 1)), __uint_as_float(r[blk][i]), acc);
+    }
+  }
+  return acc;
+}
+
+constexpr int kTStages = 4;
 
 template <int GROUPS, int LB>
 __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int L = P.L, r = P.r;
+  const int r = P.r;
+  constexpr int LP = 8 * LB;                                         // padded knot columns per key
   const uint32_t g_bytes = (uint32_t)(128 * r * 2);
-  const uint32_t t_bytes = (uint32_t)(kChunkKeys * L * r * 2);
-  const uint32_t ncols = (uint32_t)(kChunkKeys * L);               // S columns per group
-  uint8_t* g_base = smem;                                           // [group][g_bytes]
-  uint8_t* t_base = smem + (size_t)GROUPS * g_bytes;                // [2][t_bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(t_base + 2 * (size_t)t_bytes);
-  uint64_t* gfull = bars;               // [1]
-  uint64_t* tfull = gfull + 1;          // [2]
-  uint64_t* tempty = tfull + 2;         // [2]
-  uint64_t* sfull = tempty + 2;         // [GROUPS]
-  uint64_t* sempty = sfull + GROUPS;    // [GROUPS]
+  const uint32_t t_bytes = (uint32_t)(kChunkKeys * LP * r * 2);
+  constexpr uint32_t ncols = (uint32_t)(kChunkKeys * LP);            // S columns per group
+  uint8_t* g_base = smem;                                             // [group][g_bytes]
+  uint8_t* t_base = smem + (size_t)GROUPS * g_bytes;                  // [kTStages][t_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(t_base + (size_t)kTStages * t_bytes);
+  uint64_t* gfull = bars;                    // [1]
+  uint64_t* tfull = gfull + 1;               // [kTStages]
+  uint64_t* tempty = tfull + kTStages;       // [kTStages]
+  uint64_t* sfull = tempty + kTStages;       // [GROUPS]  MMA -> consumers
+  uint64_t* sempty = sfull + GROUPS;         // [GROUPS]  consumers -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty + GROUPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -173,11 +219,11 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
   const int nch = min(P.chunks_per_split, P.chunks_total - chunk_begin);
   const int64_t tile_base = (int64_t)blockIdx.x * (128 * GROUPS);
   uint32_t tmem_cols = 32;
-  while (tmem_cols < GROUPS * ncols + 8) tmem_cols <<= 1;           // +8: the last 8-column load may overhang
+  while (tmem_cols < GROUPS * ncols) tmem_cols <<= 1;
 
   if (tid == 0) {
     mbar_init(gfull, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 1); }
+    for (int i = 0; i < kTStages; ++i) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 1); }
     for (int i = 0; i < GROUPS; ++i) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 128); }
     *abort_flag = 0;
     mbar_init_fence();
@@ -202,44 +248,52 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
     float gscale, ginv;
     g_scales(*P.amax_bits, gscale, ginv);
     const float coef = P.coef * ginv;
-    const int Lm1 = L - 1;
+    const bool relu = P.act == SKV_ACT_RELU_SQ;
     const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * ncols;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
     uint4 ganext = valid && nch > 0 && garow ? __ldg(reinterpret_cast<const uint4*>(garow)) : make_uint4(0, 0, 0, 0);
 
+#ifdef SKV_TC_PROFILE
+    long long pw = 0, pl = 0;
+    const long long pstart = clock64();
+#endif
     for (int ci = 0; ci < nch; ++ci) {
       const uint4 zc = znext, gac = ganext;
       if (ci + 1 < nch && valid) {
         znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
         if (garow) ganext = __ldg(reinterpret_cast<const uint4*>(garow + (ci + 1) * kChunkKeys));
       }
-      mbar_wait(sfull + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutDz);
-      tc_fence_after();
       const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
       const uint32_t gw[4] = {gac.x, gac.y, gac.z, gac.w};
+      uint32_t bufa[LB][8], bufb[LB][8];
       float outv[kChunkKeys];
+      SKV_T(k0);
+      mbar_wait(sfull + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutDz);
+      SKV_T(k1);
+      SKV_ACC(pw, k1 - k0);
+      tc_fence_after();
+      tmem_ld_key<LB>(trow, bufa);
 #pragma unroll
       for (int q = 0; q < kChunkKeys; ++q) {
+        // the loads of key q are in flight; wait, start the loads of key q+1, then do key q's math
+        SKV_T(k2);
+        if (q & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
+        SKV_T(k3);
+        SKV_ACC(pl, k3 - k2);
+        if (q + 1 < kChunkKeys) {
+          if (q & 1) tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufa);
+          else tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufb);
+        }
         const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
         const float u = __fmul_rn(__fsub_rn(zz, P.g.lo), P.g.scale);
         const bool active = (u >= 0.0f) && (u <= P.g.Gm1f);
         const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
-        float acc = 0.0f;
-#pragma unroll
-        for (int blk = 0; blk < LB; ++blk) {
-          float v[8];
-          tmem_ld8(trow + (uint32_t)(q * L + blk * 8), v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = blk * 8 + i;           // column of this key: 0 = constant term, m>=1: T[m-1]
-            if (m == 0) acc = v[0];
-            else if (m < Lm1) acc = fmaf(__saturatef(uc - (float)(m - 1)), v[i], acc);
-          }
-        }
+        const float acc = (q & 1) ? dz_key_sum<LB>(bufb, uc) : dz_key_sum<LB>(bufa, uc);
         float o = active ? coef * acc : 0.0f;
         if (garow) {
           const float ga = (q & 1) ? bf_hi(gw[q >> 1]) : bf_lo(gw[q >> 1]);
-          o = fmaf(ga, act_grad(zz, P.act), o);
+          const float dphi = relu ? 2.0f * fmaxf(zz, 0.0f) : 1.0f;
+          o = fmaf(ga, dphi, o);
         }
         outv[q] = o;
       }
@@ -250,32 +304,58 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
             make_uint4(pack_bf2(outv[0], outv[1]), pack_bf2(outv[2], outv[3]), pack_bf2(outv[4], outv[5]),
                        pack_bf2(outv[6], outv[7]));
     }
+#ifdef SKV_TC_PROFILE
+    if (tid == 0) {
+      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+      o[0] = clock64() - pstart; o[1] = pw; o[2] = pl;
+    }
+#endif
   } else if (warp == 4 * GROUPS) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
+#ifdef SKV_TC_PROFILE
+      long long ms = 0, mt = 0, mi = 0;
+      const long long mstart = clock64();
+#endif
       mbar_wait(gfull, 0, abort_flag, P.status, kStatusTimeoutDz);
       const uint32_t rb = (uint32_t)(r / 8) * 128u;          // bytes between 8-row groups of the T image
+      const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
       for (int ci = 0; ci < nch; ++ci) {
-        const int s = ci & 1;
-        mbar_wait(tfull + s, (uint32_t)(ci >> 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        const int s = ci % kTStages;
+        SKV_T(m0);
+        mbar_wait(tfull + s, (uint32_t)(ci / kTStages) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        SKV_T(m1);
+        SKV_ACC(mt, m1 - m0);
         const uint32_t b_addr = smem_u32(t_base + (size_t)s * t_bytes);
         for (int grp = 0; grp < GROUPS; ++grp) {
+          SKV_T(m2);
           if (ci > 0) mbar_wait(sempty + grp, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+          SKV_T(m3);
+          SKV_ACC(ms, m3 - m2);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(g_base + (size_t)grp * g_bytes);
+          const uint32_t a_lo0 = desc_lo(smem_u32(g_base + (size_t)grp * g_bytes), 2048u);
           for (uint32_t c0 = 0; c0 < ncols; c0 += 256) {
             const uint32_t npiece = min(256u, ncols - c0);
             const uint32_t idesc = instr_desc(0, 0, 0, 0, 128, (int)npiece);
+            uint32_t a_lo = a_lo0;
+            uint32_t b_lo = desc_lo(b_addr + (c0 / 8) * rb, 128u);
+            const uint32_t d_addr = tmem_base + (uint32_t)grp * ncols + c0;
             for (int ks = 0; ks < r / 16; ++ks) {
-              const uint64_t ad = smem_desc(a_addr + (uint32_t)ks * 4096u, 2048u, 128u);
-              const uint64_t bd = smem_desc(b_addr + (c0 / 8) * rb + (uint32_t)ks * 256u, 128u, rb);
-              umma_f16(tmem_base + (uint32_t)grp * ncols + c0, ad, bd, idesc, ks > 0 ? 1u : 0u);
+              umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, ks > 0 ? 1u : 0u);
+              a_lo += 4096u >> 4;
+              b_lo += 256u >> 4;
             }
           }
           umma_commit(sfull + grp);
+          SKV_T(m4);
+          SKV_ACC(mi, m4 - m3);
         }
         umma_commit(tempty + s);
       }
+#ifdef SKV_TC_PROFILE
+      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+      o[4] = clock64() - mstart; o[5] = mt; o[6] = ms; o[7] = mi;
+#endif
     }
   } else {
     // ------------------------------------------------------------------ loader
@@ -287,8 +367,9 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
                  gfull);
       const uint8_t* src = reinterpret_cast<const uint8_t*>(P.timg) + (size_t)chunk_begin * t_bytes;
       for (int ci = 0; ci < nch; ++ci) {
-        const int s = ci & 1;
-        if (ci >= 2) mbar_wait(tempty + s, (uint32_t)((ci >> 1) - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        const int s = ci % kTStages;
+        if (ci >= kTStages)
+          mbar_wait(tempty + s, (uint32_t)((ci / kTStages) - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(tfull + s, t_bytes);
         bulk_g2s(t_base + (size_t)s * t_bytes, src + (size_t)ci * t_bytes, t_bytes, tfull + s);
@@ -385,9 +466,9 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
     const uint32_t t_off = (uint32_t)(t & 7) * 16u + (uint32_t)(t >> 3) * 128u;
     const uint32_t row = smem_u32(phi_base + (size_t)pg * phi_bytes) + t_off;
     const uint32_t halfL = (uint32_t)L >> 1;
-    uint32_t saved[KCH / 4];
+    uint32_t saved[KCH];
 #pragma unroll
-    for (int i = 0; i < KCH / 4; ++i) saved[i] = 0;
+    for (int i = 0; i < KCH; ++i) saved[i] = 0;
     bool have_saved = false;
     int use = 0;                                     // how often this group's stage has been filled
     for (int ti = pg; ti < ntiles; ti += 2) {
@@ -405,34 +486,25 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
         if (have_saved) {
 #pragma unroll
           for (int q = 0; q < KCH; ++q) {
-            const uint32_t w0 = (saved[q >> 2] >> ((q & 3) * 8)) & 0xffu;
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(0u) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(0u) : "memory");
+            sts32(row + (saved[q] & 0xffffu) * 4u, 0u);
+            sts32(row + (saved[q] >> 16) * 4u, 0u);
           }
           have_saved = false;
         }
         if (valid) {
-#pragma unroll
-          for (int i = 0; i < KCH / 4; ++i) saved[i] = 0;
+          const int keys_left = P.h - (key0 + ch * KCH);       // keys of this chunk that exist
 #pragma unroll
           for (int q = 0; q < KCH; ++q) {
             const uint4& zc = zq[q >> 3];
             const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
             const int qq = q & 7;
             const float zz = (qq & 1) ? bf_hi(zw[qq >> 1]) : bf_lo(zw[qq >> 1]);
-            const bool in_h = key0 + ch * KCH + q < P.h;
-            const Knot k = knot_of(zz, P.g);
-            float B0, B1, B2;
-            basis_weights(k, B0, B1, B2);
-            if (!in_h) { B0 = 0.f; B1 = 0.f; B2 = 0.f; }
-            const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
-            const bool odd = (k.bin & 1) != 0;
-            const uint32_t x0 = odd ? (p01 << 16) : p01;
-            const uint32_t x1 = odd ? __funnelshift_r(p01, p2, 16) : p2;
-            const uint32_t w0 = (uint32_t)q * halfL + ((uint32_t)k.bin >> 1);
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(x0) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(x1) : "memory");
-            saved[q >> 2] |= w0 << ((q & 3) * 8);
+            uint32_t x0, x1, wo0, wo1;
+            phi_pair(zz, P.g, (uint32_t)q * halfL, x0, x1, wo0, wo1);
+            if (q >= keys_left) { x0 = 0u; x1 = 0u; }
+            sts32(row + wo0 * 4u, x0);
+            sts32(row + wo1 * 4u, x1);
+            saved[q] = wo0 | (wo1 << 16);
           }
           have_saved = true;
         }
@@ -468,6 +540,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = instr_desc(0, 0, 1, 1, 128, r);
+      const uint32_t ab_hi = desc_hi(2048u);
       int guse[2] = {0, 0}, puse[2] = {0, 0};
       for (int tp = 0; tp < ntiles; tp += 2) {
         const int npg = min(2, ntiles - tp);
@@ -481,11 +554,17 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
             const uint32_t a_addr = smem_u32(phi_base + (size_t)pg * phi_bytes);
             const uint32_t b_addr = smem_u32(g_base + (size_t)pg * g_bytes);
             const uint32_t first = (tp == 0 && pg == 0) ? 0u : 1u;
+            const uint32_t b_lo0 = desc_lo(b_addr, 128u);
             for (int mt = 0; mt < P.mtiles; ++mt) {
-              for (int ks = 0; ks < 8; ++ks) {
-                const uint64_t ad = smem_desc(a_addr + (uint32_t)mt * 16u * 2048u + (uint32_t)ks * 256u, 128u, 2048u);
-                const uint64_t bd = smem_desc(b_addr + (uint32_t)ks * 256u, 128u, 2048u);
-                umma_f16(tmem_base + (uint32_t)((ch * P.mtiles + mt) * r), ad, bd, idesc, (first | (ks > 0)) ? 1u : 0u);
+              uint32_t a_lo = desc_lo(a_addr + (uint32_t)mt * 16u * 2048u, 128u);
+              uint32_t b_lo = b_lo0;
+              const uint32_t d_addr = tmem_base + (uint32_t)((ch * P.mtiles + mt) * r);
+              umma_f16_split(d_addr, a_lo, ab_hi, b_lo, ab_hi, idesc, first);
+#pragma unroll
+              for (int ks = 1; ks < 8; ++ks) {
+                a_lo += 256u >> 4;
+                b_lo += 256u >> 4;
+                umma_f16_split(d_addr, a_lo, ab_hi, b_lo, ab_hi, idesc, 1u);
               }
             }
             umma_commit(pempty + pg);
@@ -542,14 +621,13 @@ __global__ void tc_dc_reduce_kernel(const float* __restrict__ part, int splits, 
 struct DzPlan { int groups, lb, splits, chunks_per_split; size_t smem; };
 
 bool plan_dz(const skv_problem& p, DzPlan* o) {
-  const int ncols = kChunkKeys * p.L;
-  int groups = 2 * ncols + 8 <= 512 ? 2 : (ncols + 8 <= 512 ? 1 : 0);
-  if (!groups) return false;
-  const int lb = (p.L - 1 + 7) / 8;
-  if (lb < 1 || lb > 6 || (groups == 2 && lb > 4) || (groups == 1 && lb < 4)) return false;
+  const int lb = (p.L - 1 + 7) / 8;                  // 8-column blocks per key; columns L-1.. are padding
+  if (lb < 1 || lb > 6) return false;
+  const int ncols = kChunkKeys * 8 * lb;
+  const int groups = 2 * ncols <= 512 ? 2 : 1;
   o->groups = groups;
   o->lb = lb;
-  o->smem = (size_t)groups * 128 * p.r * 2 + 2 * (size_t)kChunkKeys * p.L * p.r * 2 + 256;
+  o->smem = (size_t)groups * 128 * p.r * 2 + (size_t)kTStages * kChunkKeys * 8 * lb * p.r * 2 + 256;
   if (o->smem > kSmemMax) return false;
   const int chunks = p.h / kChunkKeys;
   const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
@@ -559,7 +637,7 @@ bool plan_dz(const skv_problem& p, DzPlan* o) {
   for (int ks = 1; ks <= max_splits; ++ks) {
     const double waves = (double)(tiles > 0 ? tiles : 1) * ks / kPlanSMs;
     const double eff = waves / (double)(int64_t)(waves + 0.999999);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = ks; }
+    if (eff > best_eff + 0.04) { best_eff = eff; best = ks; }
   }
   o->chunks_per_split = (chunks + best - 1) / best;
   o->splits = (chunks + o->chunks_per_split - 1) / o->chunks_per_split;
@@ -593,13 +671,18 @@ bool plan_dc(const skv_problem& p, DcPlan* o) {
     for (int ns = 1; ns <= max_splits; ++ns) {
       const double waves = (double)o->slabs * ns / kPlanSMs;
       const double eff = waves / (double)(int64_t)(waves + 0.999999);
-      if (eff > best_eff + 0.02) { best_eff = eff; best = ns; }
+      if (eff > best_eff + 0.04) { best_eff = eff; best = ns; }
     }
     o->tiles_per_split = (tt + best - 1) / best;
     o->splits = (int)((tt + o->tiles_per_split - 1) / o->tiles_per_split);
     return true;
   }
   return false;
+}
+
+size_t timg_bytes(const skv_problem& p) {
+  const int lb = (p.L - 1 + 7) / 8;
+  return align256((size_t)p.h * 8 * lb * p.r * sizeof(__half));
 }
 
 size_t gimg_bytes(const skv_problem& p) {
@@ -619,7 +702,7 @@ bool bwd_eligible(const skv_problem& p) {
 size_t bwd_scratch_bytes(const skv_problem& p) {
   DcPlan d;
   if (!plan_dc(p, &d)) return 0;
-  return 256 + gimg_bytes(p) + cimg_bytes(p) + align256((size_t)d.splits * p.h * p.L * p.r * sizeof(float));
+  return 256 + gimg_bytes(p) + timg_bytes(p) + align256((size_t)d.splits * p.h * p.L * p.r * sizeof(float));
 }
 
 int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const void* g_act, int64_t gas,
@@ -634,7 +717,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
   uint32_t* amax = reinterpret_cast<uint32_t*>(base);
   __half* gimg = reinterpret_cast<__half*>(base + 256);
   __half* timg = reinterpret_cast<__half*>(base + 256 + gimg_bytes(p));
-  float* part = reinterpret_cast<float*>(base + 256 + gimg_bytes(p) + cimg_bytes(p));
+  float* part = reinterpret_cast<float*>(base + 256 + gimg_bytes(p) + timg_bytes(p));
 
   if (cudaMemsetAsync(amax, 0, 256, c.stream) != cudaSuccess) return SKV_ERR_LAUNCH;
   {
@@ -650,9 +733,9 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
   }
 
   if (dz) {
-    const size_t pieces = (size_t)p.h * p.L * (p.r / 8);
+    const size_t pieces = (size_t)p.h * 8 * zp.lb * (p.r / 8);
     const unsigned tgrid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
-    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, p.r);
+    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, 8 * zp.lb, p.r);
     note_launches(1);
     DzParams P;
     P.z = (const __nv_bfloat16*)z;
@@ -674,6 +757,9 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.chunks_total = p.h / kChunkKeys;
     P.chunks_per_split = zp.chunks_per_split;
     P.status = c.status;
+#ifdef SKV_TC_PROFILE
+    P.prof = g_prof_bwd;
+#endif
     const int64_t tiles = (p.N + 128 * zp.groups - 1) / (128 * zp.groups);
     dim3 grid((unsigned)tiles, (unsigned)zp.splits);
     const unsigned threads = 128 * zp.groups + 64;
@@ -684,7 +770,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     if (err == cudaSuccess) tc_dz_kernel<G_, LB_><<<grid, threads, zp.smem, c.stream>>>(P);                       \
   }
     SKV_DZ_CASE(2, 1) SKV_DZ_CASE(2, 2) SKV_DZ_CASE(2, 3) SKV_DZ_CASE(2, 4)
-    SKV_DZ_CASE(1, 4) SKV_DZ_CASE(1, 5) SKV_DZ_CASE(1, 6)
+    SKV_DZ_CASE(1, 5) SKV_DZ_CASE(1, 6)
 #undef SKV_DZ_CASE
     note_launches(1);
     if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }

@@ -98,6 +98,26 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the two descriptors given as 32-bit halves, so that an issue loop only has to
+// advance the low words (start address field) by a constant per K step.
+__device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Halves of an un-swizzled descriptor (see smem_desc): low word = start address and K stride,
+// high word = M/N stride and the sm_100 version bit.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) {
+  return ((addr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3FFFu) | (1u << 14); }
+
 // Arrive on `bar` when every MMA this thread has issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -148,6 +168,39 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
 }
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// ---------------------------------------------------------------------------------------------
+// Expanded-basis (Phi) row segment of one (token, key) pair.
+//
+// A token's Phi row is stored K-major in the un-swizzled canonical layout: 32-bit word w of the
+// row (knot columns 2w, 2w+1 as f16x2) lives at byte (w >> 2) * 2048 + (w & 3) * 4 from the
+// token's row base, i.e. at word offset w + (w >> 2) * 508.  The three non-zero weights sit at
+// columns bin..bin+2 of the key's L columns and always fall into two consecutive words.
+// phi_pair returns those two words and their word offsets; `wq` is the word index at which the
+// key's segment starts (key-in-chunk * L / 2).
+// The weights use B1 = 1 - B0 - B2 (partition of unity), masked by 0 <= u <= G.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t wq, uint32_t& x0, uint32_t& x1,
+                                         uint32_t& wo0, uint32_t& wo1) {
+  const Knot k = knot_of(zz, g);
+  const float t = k.tau, omt = 1.0f - t;
+  const float m = k.in_range ? 1.0f : 0.0f;
+  const float hm = k.in_range ? 0.5f : 0.0f;
+  const float B0 = (hm * omt) * omt;
+  const float B2 = (hm * t) * t;
+  const float B1 = (m - B0) - B2;
+  const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
+  const uint32_t sh = ((uint32_t)k.bin & 1u) << 4;
+  x0 = p01 << sh;
+  x1 = __funnelshift_l(p01, p2, sh);
+  const uint32_t s0 = wq + ((uint32_t)k.bin >> 1), s1 = s0 + 1u;
+  wo0 = s0 + (s0 >> 2) * 508u;
+  wo1 = s1 + (s1 >> 2) * 508u;
+}
+
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 
 }  // namespace tc
 }  // namespace skv

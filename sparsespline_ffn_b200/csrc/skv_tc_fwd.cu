@@ -28,9 +28,10 @@ namespace tc {
 namespace {
 
 constexpr int kStages = 2;
+constexpr int kMaxCStages = 4;
 constexpr int kChunkKeys = 8;
 constexpr int kPlanSMs = 148;                 // B200; only used to balance the launch shape
-constexpr size_t kSmemLimit = 220 * 1024;
+constexpr size_t kSmemLimit = 227 * 1024;
 
 struct FwdParams {
   const __nv_bfloat16* z;
@@ -46,6 +47,10 @@ struct FwdParams {
   int chunks_total, chunks_per_split;
   int32_t* status;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
+  int cstages;              // depth of the code-table ring (2..4)
+#ifdef SKV_TC_PROFILE
+  long long* prof;          // [ctas][8] phase cycle counters (diagnostic builds only)
+#endif
 };
 
 __device__ __forceinline__ uint32_t word_off(uint32_t w) { return (w >> 2) * 2048u + (w & 3u) * 4u; }
@@ -57,13 +62,14 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
   const uint32_t phi_bytes = (uint32_t)L * 2048u;                 // 128 tokens x 8L f16
   const uint32_t c_bytes = (uint32_t)(kChunkKeys * L * r * 2);
   uint8_t* phi_base = smem;                                        // [stage][group][phi_bytes]
-  uint8_t* c_base = smem + (size_t)kStages * GROUPS * phi_bytes;   // [stage][c_bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(c_base + (size_t)kStages * c_bytes);
+  const int CS = P.cstages;
+  uint8_t* c_base = smem + (size_t)kStages * GROUPS * phi_bytes;   // [cstage][c_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(c_base + (size_t)CS * c_bytes);
   uint64_t* full = bars;                          // [stage][group]   producers -> MMA
   uint64_t* empty = full + kStages * GROUPS;      // [stage][group]   MMA -> producers
-  uint64_t* cfull = empty + kStages * GROUPS;     // [stage]          TMA -> MMA
-  uint64_t* cempty = cfull + kStages;             // [stage]          MMA -> TMA
-  uint64_t* done = cempty + kStages;              // [1]
+  uint64_t* cfull = empty + kStages * GROUPS;     // [cstage]         TMA -> MMA
+  uint64_t* cempty = cfull + kMaxCStages;         // [cstage]         MMA -> TMA
+  uint64_t* done = cempty + kMaxCStages;          // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -76,7 +82,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 
   if (tid == 0) {
     for (int i = 0; i < kStages * GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); }
-    for (int i = 0; i < kStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, 1); }
+    for (int i = 0; i < kMaxCStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, 1); }
     mbar_init(done, 1);
     *abort_flag = 0;
     mbar_init_fence();
@@ -104,53 +110,67 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
     const __nv_bfloat16* zrow = P.z + (valid ? n : 0) * P.zs + (int64_t)chunk_begin * kChunkKeys;
     __nv_bfloat16* arow = P.act_out ? P.act_out + (valid ? n : 0) * P.as + (int64_t)chunk_begin * kChunkKeys : nullptr;
     const uint32_t halfL = (uint32_t)L >> 1;
-    uint32_t saved[kStages][2] = {{0, 0}, {0, 0}};
+    uint32_t saved[kStages][kChunkKeys];
+#pragma unroll
+    for (int i = 0; i < kStages; ++i)
+#pragma unroll
+      for (int q = 0; q < kChunkKeys; ++q) saved[i][q] = 0;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
+    const bool relu = P.act == SKV_ACT_RELU_SQ;
 
-    auto chunk_body = [&](int ci, int s, uint32_t(&sv)[2]) {
+#ifdef SKV_TC_PROFILE
+    long long pw = 0, pb = 0, pf = 0;
+    const long long pstart = clock64();
+#define SKV_T(x) const long long x = clock64()
+#else
+#define SKV_T(x)
+#endif
+    auto chunk_body = [&](int ci, int s, uint32_t(&sv)[kChunkKeys]) {
+      SKV_T(c0);
       const uint4 zc = znext;
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
       const uint32_t row = smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes) + t_off;
       if (ci >= kStages) {
         mbar_wait(empty + s * GROUPS + grp, (uint32_t)((ci / kStages) - 1) & 1u, abort_flag, P.status,
                   kStatusTimeoutFwd);
+        SKV_T(c1);
+#ifdef SKV_TC_PROFILE
+        pw += c1 - c0;
+#endif
         if (valid) {
 #pragma unroll
           for (int q = 0; q < kChunkKeys; ++q) {
-            const uint32_t w0 = (sv[q >> 2] >> ((q & 3) * 8)) & 0xffu;
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(0u) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(0u) : "memory");
+            sts32(row + (sv[q] & 0xffffu) * 4u, 0u);
+            sts32(row + (sv[q] >> 16) * 4u, 0u);
           }
         }
       }
       if (valid) {
         const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
         uint32_t aw[4];
-        uint32_t nsv[2] = {0, 0};
 #pragma unroll
         for (int q = 0; q < kChunkKeys; ++q) {
           const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
-          const Knot k = knot_of(zz, P.g);
-          float B0, B1, B2;
-          basis_weights(k, B0, B1, B2);
-          const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
-          const bool odd = (k.bin & 1) != 0;
-          const uint32_t x0 = odd ? (p01 << 16) : p01;
-          const uint32_t x1 = odd ? __funnelshift_r(p01, p2, 16) : p2;
-          const uint32_t w0 = (uint32_t)q * halfL + ((uint32_t)k.bin >> 1);
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0)), "r"(x0) : "memory");
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(row + word_off(w0 + 1)), "r"(x1) : "memory");
-          nsv[q >> 2] |= w0 << ((q & 3) * 8);
-          const float a = act_fwd(zz, P.act);
+          uint32_t x0, x1, wo0, wo1;
+          phi_pair(zz, P.g, (uint32_t)q * halfL, x0, x1, wo0, wo1);
+          sts32(row + wo0 * 4u, x0);
+          sts32(row + wo1 * 4u, x1);
+          sv[q] = wo0 | (wo1 << 16);
+          const float zp = fmaxf(zz, 0.0f);
+          const float a = relu ? zp * zp : zz;
           if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
           else aw[q >> 1] = __float_as_uint(a);
         }
-        sv[0] = nsv[0];
-        sv[1] = nsv[1];
         if (arow) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
       }
+      SKV_T(c2);
       fence_async_smem();
       mbar_arrive(full + s * GROUPS + grp);
+#ifdef SKV_TC_PROFILE
+      const long long c3 = clock64();
+      pf += c3 - c2;
+      pb += c2 - c0;
+#endif
     };
 
     for (int ci = 0; ci < nch; ci += kStages) {
@@ -158,6 +178,12 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
       if (ci + 1 < nch) chunk_body(ci + 1, 1, saved[1]);
     }
 
+#ifdef SKV_TC_PROFILE
+    if (tid == 0) {
+      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+      o[0] = clock64() - pstart; o[1] = pw; o[2] = pb; o[3] = pf;
+    }
+#endif
     // epilogue: accumulator -> float32 partial of this key split
     mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutFwd);
     tc_fence_after();
@@ -178,34 +204,60 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
     if (lane == 0) {
       const uint32_t idesc = instr_desc(0, 0, 0, 1, 128, r);
       const int ksteps = kChunkKeys * L / 16;
+      const uint32_t a_hi = desc_hi(P.a_sbo), b_hi = desc_hi(P.b_sbo);
+      const uint32_t a_step = (2u * 2048u) >> 4, b_step = (2u * (uint32_t)(r / 8) * 128u) >> 4;   // per K=16 step
+#ifdef SKV_TC_PROFILE
+      long long mc = 0, mf = 0, mi = 0;
+      const long long mstart = clock64();
+#endif
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % kStages;
         const uint32_t par = (uint32_t)(ci / kStages) & 1u;
-        mbar_wait(cfull + s, par, abort_flag, P.status, kStatusTimeoutFwd);
-        const uint32_t b_addr = smem_u32(c_base + (size_t)s * c_bytes);
+        const int cs = ci % CS;
+        SKV_T(m0);
+        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        SKV_T(m1);
+#ifdef SKV_TC_PROFILE
+        mc += m1 - m0;
+#endif
+        const uint32_t b_lo0 = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
         for (int grp = 0; grp < GROUPS; ++grp) {
+          SKV_T(m2);
           mbar_wait(full + s * GROUPS + grp, par, abort_flag, P.status, kStatusTimeoutFwd);
+          SKV_T(m3);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes);
-          for (int ks = 0; ks < ksteps; ++ks) {
-            const uint64_t ad = smem_desc(a_addr + (uint32_t)ks * 2u * 2048u, P.a_lbo, P.a_sbo);
-            const uint64_t bd = smem_desc(b_addr + (uint32_t)ks * 2u * (uint32_t)(r / 8) * 128u, P.b_lbo, P.b_sbo);
-            umma_f16(tmem_base + (uint32_t)(grp * r), ad, bd, idesc, (ci > 0 || ks > 0) ? 1u : 0u);
+          uint32_t a_lo = desc_lo(smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes), P.a_lbo);
+          uint32_t b_lo = b_lo0;
+          const uint32_t d_addr = tmem_base + (uint32_t)(grp * r);
+          umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, ci > 0 ? 1u : 0u);
+          for (int ks = 1; ks < ksteps; ++ks) {
+            a_lo += a_step;
+            b_lo += b_step;
+            umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, 1u);
           }
           umma_commit(empty + s * GROUPS + grp);
+#ifdef SKV_TC_PROFILE
+          const long long m4 = clock64();
+          mf += m3 - m2;
+          mi += m4 - m3;
+#endif
         }
-        umma_commit(cempty + s);
+        umma_commit(cempty + cs);
       }
       umma_commit(done);
+#ifdef SKV_TC_PROFILE
+      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+      o[4] = clock64() - mstart; o[5] = mc; o[6] = mf; o[7] = mi;
+#endif
     }
   } else {
     // ------------------------------------------------------------------ code-table loader
     if (lane == 0) {
       const uint8_t* src = reinterpret_cast<const uint8_t*>(P.cimg) + (size_t)chunk_begin * c_bytes;
       for (int ci = 0; ci < nch; ++ci) {
-        const int s = ci % kStages;
-        if (ci >= kStages)
-          mbar_wait(cempty + s, (uint32_t)((ci / kStages) - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        const int s = ci % CS;
+        if (ci >= CS)
+          mbar_wait(cempty + s, (uint32_t)((ci / CS) - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(cfull + s, c_bytes);
         bulk_g2s(c_base + (size_t)s * c_bytes, src + (size_t)ci * c_bytes, c_bytes, cfull + s);
@@ -259,20 +311,29 @@ __global__ void tc_finalize_kernel(const float* __restrict__ partial, int splits
   }
 }
 
+#ifdef SKV_TC_PROFILE
+}  // namespace
+long long* g_prof = nullptr;   // set by the diagnostic harness before calling forward()
+namespace {
+#endif
+
 struct FwdPlan {
-  int groups, splits, chunks_per_split;
+  int groups, splits, chunks_per_split, cstages;
   size_t smem;
 };
 
-size_t fwd_smem(int groups, int L, int r) {
-  return (size_t)kStages * groups * L * 2048 + (size_t)kStages * kChunkKeys * L * r * 2 + 256;
+size_t fwd_smem(int groups, int cstages, int L, int r) {
+  return (size_t)kStages * groups * L * 2048 + (size_t)cstages * kChunkKeys * L * r * 2 + 256;
 }
 
 bool plan_forward(const skv_problem& p, FwdPlan* out) {
   int groups = 0;
-  if (fwd_smem(2, p.L, p.r) <= kSmemLimit) groups = 2;
-  else if (fwd_smem(1, p.L, p.r) <= kSmemLimit) groups = 1;
+  if (fwd_smem(2, 2, p.L, p.r) <= kSmemLimit) groups = 2;
+  else if (fwd_smem(1, 2, p.L, p.r) <= kSmemLimit) groups = 1;
   if (!groups) return false;
+  int cstages = 2;
+  while (cstages < kMaxCStages && fwd_smem(groups, cstages + 1, p.L, p.r) <= kSmemLimit) ++cstages;
+  out->cstages = cstages;
   const int chunks = p.h / kChunkKeys;
   const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
   int best = 1;
@@ -281,13 +342,13 @@ bool plan_forward(const skv_problem& p, FwdPlan* out) {
   for (int ks = 1; ks <= max_splits; ++ks) {
     const double waves = (double)(tiles > 0 ? tiles : 1) * ks / kPlanSMs;
     const double eff = waves / (double)(int64_t)(waves + 0.999999);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = ks; }
+    if (eff > best_eff + 0.04) { best_eff = eff; best = ks; }
   }
   out->groups = groups;
   out->splits = best;
   out->chunks_per_split = (chunks + best - 1) / best;
   out->splits = (chunks + out->chunks_per_split - 1) / out->chunks_per_split;
-  out->smem = fwd_smem(groups, p.L, p.r);
+  out->smem = fwd_smem(groups, cstages, p.L, p.r);
   return true;
 }
 
@@ -346,6 +407,10 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.chunks_total = p.h / kChunkKeys;
   P.chunks_per_split = f.chunks_per_split;
   P.status = c.status;
+  P.cstages = f.cstages;
+#ifdef SKV_TC_PROFILE
+  P.prof = g_prof;
+#endif
   // A: Phi tile, K-major; core matrices of 8 tokens x 8 k: 128 B apart along tokens, 2048 B along k
   P.a_lbo = 2048;
   P.a_sbo = 128;
