@@ -179,18 +179,27 @@ __device__ __forceinline__ void tmem_wait_key(uint32_t (&r)[LB][8]) {
 
 // S_0 + sum_m sat(uc - m) * S_{m+1} over the 8*LB columns of one key (padding columns are zero in
 // the table image and their weight sat(uc - m) is zero as well, since uc <= G-1 < m).
+// Columns are taken in aligned pairs with the packed two-wide float32 FMA of sm_100
+// (fma.rn.f32x2): weight 1 for column 0, sat(uc - (m-1)) for column m.
 template <int LB>
 __device__ __forceinline__ float dz_key_sum(const uint32_t (&r)[LB][8], float uc) {
-  float acc = __uint_as_float(r[0][0]);
+  unsigned long long acc2 = 0ull;                     // (0.0f, 0.0f)
 #pragma unroll
   for (int blk = 0; blk < LB; ++blk) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 8; i += 2) {
       const int m = blk * 8 + i;
-      if (m > 0) acc = fmaf(__saturatef(uc - (float)(m - 1)), __uint_as_float(r[blk][i]), acc);
+      const float w0 = m == 0 ? 1.0f : __saturatef(uc - (float)(m - 1));
+      const float w1 = __saturatef(uc - (float)m);
+      unsigned long long w2, s2;
+      asm("mov.b64 %0, {%1, %2};" : "=l"(w2) : "f"(w0), "f"(w1));
+      asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[blk][i]), "r"(r[blk][i + 1]));
+      asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2) : "l"(w2), "l"(s2));
     }
   }
-  return acc;
+  float a0, a1;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc2));
+  return a0 + a1;
 }
 
 constexpr int kTStages = 4;

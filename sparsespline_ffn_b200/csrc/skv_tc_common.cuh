@@ -118,6 +118,19 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) {
 }
 __device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3FFFu) | (1u << 14); }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (lane = row of A,
+// each 32-bit column holds two consecutive K elements), B from shared memory.
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Arrive on `bar` when every MMA this thread has issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -197,6 +210,61 @@ __device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t
   wo0 = s0 + (s0 >> 2) * 508u;
   wo1 = s1 + (s1 >> 2) * 508u;
 }
+
+// Knot-dependent part of phi_pair only: the two f16x2 words and the index (bin >> 1) of the first
+// one within the key's L/2 words.
+__device__ __forceinline__ void phi_pair_words(float zz, const GridParams& g, uint32_t& x0, uint32_t& x1,
+                                               uint32_t& wp) {
+  const Knot k = knot_of(zz, g);
+  const float t = k.tau, omt = 1.0f - t;
+  const float m = k.in_range ? 1.0f : 0.0f;
+  const float hm = k.in_range ? 0.5f : 0.0f;
+  const float B0 = (hm * omt) * omt;
+  const float B2 = (hm * t) * t;
+  const float B1 = (m - B0) - B2;
+  const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
+  const uint32_t sh = ((uint32_t)k.bin & 1u) << 4;
+  x0 = p01 << sh;
+  x1 = __funnelshift_l(p01, p2, sh);
+  wp = (uint32_t)k.bin >> 1;
+}
+
+// Store N consecutive 32-bit columns of this thread's tensor-memory lane (lane = 32 * (warp % 4) + lane id).
+template <int N> __device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t* w);
+template <> __device__ __forceinline__ void tmem_st<1>(uint32_t taddr, const uint32_t* w) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(w[0]) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_st<2>(uint32_t taddr, const uint32_t* w) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(w[0]), "r"(w[1]) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_st<4>(uint32_t taddr, const uint32_t* w) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(w[0]), "r"(w[1]),
+               "r"(w[2]), "r"(w[3])
+               : "memory");
+}
+template <> __device__ __forceinline__ void tmem_st<8>(uint32_t taddr, const uint32_t* w) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(w[0]),
+               "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+template <> __device__ __forceinline__ void tmem_st<16>(uint32_t taddr, const uint32_t* w) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16};" ::"r"(taddr),
+      "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]), "r"(w[9]),
+      "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
+      : "memory");
+}
+// HL (< 32) consecutive columns as the binary decomposition of HL into x16/x8/x4/x2/x1 stores.
+template <int HL> __device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t* w) {
+  int o = 0;
+  if constexpr ((HL & 16) != 0) { tmem_st<16>(taddr + o, w + o); o += 16; }
+  if constexpr ((HL & 8) != 0) { tmem_st<8>(taddr + o, w + o); o += 8; }
+  if constexpr ((HL & 4) != 0) { tmem_st<4>(taddr + o, w + o); o += 4; }
+  if constexpr ((HL & 2) != 0) { tmem_st<2>(taddr + o, w + o); o += 2; }
+  if constexpr ((HL & 1) != 0) { tmem_st<1>(taddr + o, w + o); o += 1; }
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");

@@ -29,6 +29,7 @@ namespace {
 
 constexpr int kStages = 2;
 constexpr int kMaxCStages = 4;
+constexpr int kMaxTaCStages = 8;
 constexpr int kChunkKeys = 8;
 constexpr int kPlanSMs = 148;                 // B200; only used to balance the launch shape
 constexpr size_t kSmemLimit = 227 * 1024;
@@ -279,6 +280,204 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward with the expanded basis held in tensor memory instead of shared memory.
+//
+// The shared-memory variant above is bound by shared-memory bandwidth: every MMA re-reads its
+// 4 KB A tile while the producers scatter words into the same banks.  Here each producer thread
+// builds the complete Phi row segment of a key (HL = L/2 f16x2 words, two of them non-zero) in
+// registers and writes it with tcgen05.st into its own tensor-memory lane; the MMA takes A from
+// tensor memory and only the code-table chunk (B) from shared memory.  Nothing has to be
+// cleared: a row segment is overwritten completely every chunk.
+//
+// Tensor-memory columns per token group: 8*HL for A (single-buffered) followed by r for the
+// accumulator; with four groups (512 tokens per CTA, 16 producer warps) the other groups keep the
+// SM busy while one group waits for its MMAs.
+// ---------------------------------------------------------------------------------------------
+template <int GROUPS, int HL>
+__global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(const FwdParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int L = 2 * HL, r = P.r;
+  const uint32_t c_bytes = (uint32_t)(kChunkKeys * L * r * 2);
+  const int CS = P.cstages;
+  uint8_t* c_base = smem;                                          // [cstage][c_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(c_base + (size_t)CS * c_bytes);
+  uint64_t* full = bars;                          // [group]    producers -> MMA
+  uint64_t* empty = full + GROUPS;                // [group]    MMA -> producers
+  uint64_t* cfull = empty + GROUPS;               // [cstage]   TMA -> MMA
+  uint64_t* cempty = cfull + kMaxTaCStages;       // [cstage]   MMA -> TMA
+  uint64_t* done = cempty + kMaxTaCStages;        // [group]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + GROUPS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunk_begin = blockIdx.y * P.chunks_per_split;
+  const int nch = min(P.chunks_per_split, P.chunks_total - chunk_begin);
+  const int64_t tile_base = (int64_t)blockIdx.x * (128 * GROUPS);
+  const uint32_t grp_cols = (uint32_t)(kChunkKeys * HL + r);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < GROUPS * grp_cols) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int i = 0; i < GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); mbar_init(done + i, 1); }
+    for (int i = 0; i < kMaxTaCStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, GROUPS); }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 5 * GROUPS) tmem_alloc(tmem_slot, tmem_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4 * GROUPS) {
+    // ------------------------------------------------------------------ producers / epilogue
+    const int grp = warp >> 2;
+    const int t = tid & 127;
+    const int64_t n = tile_base + grp * 128 + t;
+    const bool valid = n < P.N;
+    const __nv_bfloat16* zrow = P.z + (valid ? n : 0) * P.zs + (int64_t)chunk_begin * kChunkKeys;
+    __nv_bfloat16* arow = P.act_out ? P.act_out + (valid ? n : 0) * P.as + (int64_t)chunk_begin * kChunkKeys : nullptr;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
+    const bool relu = P.act == SKV_ACT_RELU_SQ;
+    uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
+
+#ifdef SKV_TC_PROFILE
+    long long pw = 0, pb = 0, pf = 0;
+    const long long pstart = clock64();
+#endif
+    for (int ci = 0; ci < nch; ++ci) {
+      SKV_T(c0);
+      const uint4 zc = znext;
+      if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
+      const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
+      uint32_t aw[4];
+      if (ci > 0) {
+        mbar_wait(empty + grp, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        tc_fence_after();
+      }
+      SKV_T(c1);
+#pragma unroll
+      for (int q = 0; q < kChunkKeys; ++q) {
+        const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+        uint32_t x0, x1, wp;
+        phi_pair_words(valid ? zz : __int_as_float(0x7fc00000), P.g, x0, x1, wp);   // NaN row: all weights zero
+        uint32_t W[HL];
+        W[0] = wp == 0u ? x0 : 0u;
+#pragma unroll
+        for (int i = 1; i < HL - 1; ++i) W[i] = wp == (uint32_t)i ? x0 : (wp == (uint32_t)(i - 1) ? x1 : 0u);
+        W[HL - 1] = wp == (uint32_t)(HL - 2) ? x1 : 0u;
+        tmem_st_words<HL>(lane_addr + (uint32_t)(q * HL), W);
+        const float zp = fmaxf(zz, 0.0f);
+        const float a = relu ? zp * zp : zz;
+        if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
+        else aw[q >> 1] = __float_as_uint(a);
+      }
+      SKV_T(c2);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(full + grp);
+#ifdef SKV_TC_PROFILE
+      const long long c3 = clock64();
+      pw += c1 - c0; pb += c2 - c1; pf += c3 - c2;
+#endif
+      if (arow && valid) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+    }
+
+#ifdef SKV_TC_PROFILE
+    if (tid == 0) {
+      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+      o[0] = clock64() - pstart; o[1] = pw; o[2] = pb; o[3] = pf;
+    }
+#endif
+    // epilogue: accumulator -> float32 partial of this key split
+    mbar_wait(done + grp, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    tc_fence_after();
+    float* prow = P.partial + ((size_t)blockIdx.y * P.N + (valid ? n : 0)) * r;
+    const uint32_t daddr = lane_addr + (uint32_t)(kChunkKeys * HL);
+    for (int c0 = 0; c0 < r; c0 += 16) {
+      float v[16];
+      tmem_ld16(daddr + c0, v);
+      if (valid) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4)
+          *reinterpret_cast<float4*>(prow + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      }
+    }
+    tc_fence_before();
+  } else if (warp < 5 * GROUPS) {
+    // ------------------------------------------------------------------ MMA issue, one warp per token group
+    // (a single issuing thread for all groups is starved of issue slots by the producer warps)
+    if (lane == 0) {
+      const int grp = warp - 4 * GROUPS;
+      const uint32_t idesc = instr_desc(0, 0, 0, 1, 128, r);
+      const uint32_t b_hi = desc_hi(P.b_sbo);
+      const uint32_t b_step = (2u * (uint32_t)(r / 8) * 128u) >> 4;          // per K=16 step
+      const uint32_t a_addr0 = tmem_base + (uint32_t)grp * grp_cols;
+      const uint32_t d_addr = a_addr0 + (uint32_t)(kChunkKeys * HL);
+#ifdef SKV_TC_PROFILE
+      long long mc = 0, mf = 0, mi = 0;
+      const long long mstart = clock64();
+#endif
+      for (int ci = 0; ci < nch; ++ci) {
+        const int cs = ci % CS;
+        SKV_T(m0);
+        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        SKV_T(m1);
+        mbar_wait(full + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        SKV_T(m3);
+        tc_fence_after();
+        uint32_t a_addr = a_addr0;
+        uint32_t b_lo = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
+        umma_f16_ta(d_addr, a_addr, b_lo, b_hi, idesc, ci > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 1; ks < HL; ++ks) {            // 8*L/16 = HL steps of K = 16 (8 columns of A each)
+          a_addr += 8u;
+          b_lo += b_step;
+          umma_f16_ta(d_addr, a_addr, b_lo, b_hi, idesc, 1u);
+        }
+        umma_commit(empty + grp);
+        umma_commit(cempty + cs);
+#ifdef SKV_TC_PROFILE
+        const long long m4 = clock64();
+        mc += m1 - m0; mf += m3 - m1; mi += m4 - m3;
+#endif
+      }
+      umma_commit(done + grp);
+#ifdef SKV_TC_PROFILE
+      if (grp == 0) {
+        long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+        o[4] = clock64() - mstart; o[5] = mc; o[6] = mf; o[7] = mi;
+      }
+#endif
+    }
+  } else {
+    // ------------------------------------------------------------------ code-table loader
+    if (lane == 0) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(P.cimg) + (size_t)chunk_begin * c_bytes;
+      for (int ci = 0; ci < nch; ++ci) {
+        const int s = ci % CS;
+        if (ci >= CS)
+          mbar_wait(cempty + s, (uint32_t)((ci / CS) - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(cfull + s, c_bytes);
+        bulk_g2s(c_base + (size_t)s * c_bytes, src + (size_t)ci * c_bytes, c_bytes, cfull + s);
+      }
+      if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 5 * GROUPS) {
+    for (int i = 0; i < GROUPS; ++i) mbar_wait(done + i, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    tc_fence_after();
+    tmem_free(tmem_base, tmem_cols);
+  }
+}
+
 // C [h][L][r] bf16 -> f16 image: per 8-key chunk the [8L x r] tile as 8x8 core matrices,
 // core (kg, cg) at ((kg * r/8 + cg) * 128) bytes, row k%8 at 16 bytes, channel c%8 at 2 bytes.
 __global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int r) {
@@ -320,13 +519,45 @@ namespace {
 struct FwdPlan {
   int groups, splits, chunks_per_split, cstages;
   size_t smem;
+  bool ta;                  // expanded basis in tensor memory (tc_forward_ta_kernel) instead of shared memory
 };
+
+// Half knot-row counts (L/2) the tensor-memory variant is instantiated for.
+bool ta_supported_hl(int hl) { return hl == 8 || hl == 11 || hl == 21; }
 
 size_t fwd_smem(int groups, int cstages, int L, int r) {
   return (size_t)kStages * groups * L * 2048 + (size_t)cstages * kChunkKeys * L * r * 2 + 256;
 }
 
 bool plan_forward(const skv_problem& p, FwdPlan* out) {
+  out->ta = false;
+  const int hl = p.L / 2;
+  if (p.L % 2 == 0 && ta_supported_hl(hl) && kChunkKeys * hl + p.r <= 512) {
+    int groups = 512 / (kChunkKeys * hl + p.r);
+    if (groups > 4) groups = 4;
+    const size_t c_bytes = (size_t)kChunkKeys * p.L * p.r * 2;
+    int cstages = (int)((kSmemLimit - 256) / c_bytes);
+    if (cstages > kMaxTaCStages) cstages = kMaxTaCStages;
+    if (cstages >= 2) {
+      out->ta = true;
+      out->groups = groups;
+      out->cstages = cstages;
+      out->smem = (size_t)cstages * c_bytes + 256;
+      const int chunks = p.h / kChunkKeys;
+      const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
+      int best = 1;
+      double best_eff = 0.0;
+      const int max_splits = chunks >= 16 ? (chunks / 8 < 16 ? chunks / 8 : 16) : 1;
+      for (int ks = 1; ks <= max_splits; ++ks) {
+        const double waves = (double)(tiles > 0 ? tiles : 1) * ks / kPlanSMs;
+        const double eff = waves / (double)(int64_t)(waves + 0.999999);
+        if (eff > best_eff + 0.04) { best_eff = eff; best = ks; }
+      }
+      out->chunks_per_split = (chunks + best - 1) / best;
+      out->splits = (chunks + out->chunks_per_split - 1) / out->chunks_per_split;
+      return true;
+    }
+  }
   int groups = 0;
   if (fwd_smem(2, 2, p.L, p.r) <= kSmemLimit) groups = 2;
   else if (fwd_smem(1, 2, p.L, p.r) <= kSmemLimit) groups = 1;
@@ -420,8 +651,20 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
 
   const int64_t tiles = (p.N + 128 * f.groups - 1) / (128 * f.groups);
   dim3 grid((unsigned)tiles, (unsigned)f.splits);
-  cudaError_t err;
-  if (f.groups == 2) {
+  cudaError_t err = cudaErrorInvalidValue;
+  if (f.ta) {
+    const unsigned threads = 160 * f.groups + 32;
+    const int hl = p.L / 2;
+#define SKV_TA_CASE(G_, HL_)                                                                                         \
+  if (f.groups == G_ && hl == HL_) {                                                                                 \
+    err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem); \
+    if (err == cudaSuccess) tc_forward_ta_kernel<G_, HL_><<<grid, threads, f.smem, c.stream>>>(P);                   \
+  }
+    SKV_TA_CASE(1, 8) SKV_TA_CASE(2, 8) SKV_TA_CASE(3, 8) SKV_TA_CASE(4, 8)
+    SKV_TA_CASE(1, 11) SKV_TA_CASE(2, 11) SKV_TA_CASE(3, 11) SKV_TA_CASE(4, 11)
+    SKV_TA_CASE(1, 21) SKV_TA_CASE(2, 21)
+#undef SKV_TA_CASE
+  } else if (f.groups == 2) {
     err = cudaFuncSetAttribute(tc_forward_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem);
     if (err == cudaSuccess) tc_forward_kernel<2><<<grid, 128 * 2 + 64, f.smem, c.stream>>>(P);
   } else {
