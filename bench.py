@@ -47,19 +47,47 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU while a region runs (read-only NVML queries
+    from a thread every few milliseconds; nvidia-smi in a loop if the NVML binding is missing)."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.index, self.rows, self.proc, self.thread, self.stop_flag = index, [], None, None, False
+        self.sm, self.smax, self.reasons = [], [], set()
+
+    def _nvml_loop(self, nvml, handle):
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
+                mask = int(nvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(0.004)
 
     def start(self):
         try:
+            import pynvml as nvml
+            nvml.nvmlInit()
+            # NVML orders devices by PCI bus id, as CUDA does when CUDA_VISIBLE_DEVICES is unset
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
+            handle = nvml.nvmlDeviceGetHandleByIndex(idx)
+            self.smax.append(float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -71,29 +99,29 @@ class ClockSampler:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def stop(self):
-        if self.proc is None:
-            return None
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        self.stop_flag = True
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
         if self.thread:
             self.thread.join(timeout=2)
-        sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             try:
-                sm.append(float(r[0]))
-                smax.append(float(r[1]))
+                self.sm.append(float(r[0]))
+                self.smax.append(float(r[1]))
             except (ValueError, IndexError):
                 continue
             for name, val in zip(names, r[4:8]):
                 if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+                    self.reasons.add(name)
+        if not self.sm:
             return None
-        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        return dict(sm_mhz=statistics.median(self.sm), sm_max_mhz=max(self.smax) if self.smax else None,
+                    reasons=sorted(self.reasons), samples=len(self.sm))
 
 
 def cpu_port_tokens_per_s(cfg, seed, target_seconds=12.0):
@@ -164,7 +192,7 @@ def make_cfg(gpus):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling of small cases)")

@@ -1,0 +1,77 @@
+"""The d20 production shape (N = 65536 tokens, h = 5120, G = 20, r = 32, bf16) on the GPU.
+
+At this size the oracle is applied where it finishes in seconds (the C/OpenMP restatement on all
+tokens for dC, a token subset for f and dz) and size-independent properties cover the rest:
+exact linearity in C, exact zeros, bitwise run-to-run determinism.
+"""
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+ops = pytest.importorskip("sparsespline_ffn_b200.ops")
+
+N, H, R, G = 65536, 5120, 32, 20
+LO, HI = -5.0, 5.0
+
+
+@pytest.fixture(scope="module")
+def data():
+    g = torch.Generator(device="cuda").manual_seed(5)
+    z = (torch.randn(N, H, generator=g, device="cuda") * 1.5).to(torch.bfloat16)
+    C = (torch.randn(H, G + 2, R, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    go = torch.randn(N, H + R, generator=g, device="cuda").to(torch.bfloat16)
+    return z, C, go
+
+
+def test_forward_properties_and_sampled_parity(data):
+    z, C, _ = data
+    assert ops.resolve_impl(z, C, LO, HI, G) == "tcgen05"
+    f = ops.feature_forward(z, C, LO, HI, G, "relu_sq", 1.0)
+    # bitwise determinism
+    assert torch.equal(f, ops.feature_forward(z, C, LO, HI, G, "relu_sq", 1.0))
+    # exact linearity in C: a power of two commutes with every rounding on the path as long as no
+    # table entry is an f16 subnormal, so use entries k * 2^-12 with |k| <= 127
+    gq = torch.Generator(device="cuda").manual_seed(6)
+    Cq = (torch.randint(-127, 128, C.shape, generator=gq, device="cuda").float() / 4096).to(torch.bfloat16)
+    f1 = ops.feature_forward(z, Cq, LO, HI, G, "relu_sq", 1.0)
+    f2 = ops.feature_forward(z, Cq * 2, LO, HI, G, "relu_sq", 1.0)
+    assert torch.equal(f2[:, H:].float(), 2 * f1[:, H:].float())
+    assert torch.equal(f2[:, :H], f[:, :H])
+    # exact zeros
+    f0 = ops.feature_forward(z, torch.zeros_like(C), LO, HI, G, "relu_sq", 1.0)
+    assert torch.count_nonzero(f0[:, H:]) == 0
+    # a token subset against the oracle; indices bit for bit
+    idx = torch.randperm(N, generator=torch.Generator().manual_seed(1))[:512].cuda()
+    zs = z[idx].contiguous()
+    assert np.array_equal(ops.knot_index(zs, LO, HI, G).cpu().numpy(), util.oc.knot_index(util.f32(zs), LO, HI, G))
+    a_ref, d_ref = util.oracle_forward(zs, C, LO, HI, G, "relu_sq", 1.0)
+    util.assert_parity("phi(z)", f[idx][:, :H], a_ref, torch.bfloat16)
+    util.assert_parity("delta", f[idx][:, H:], d_ref, torch.bfloat16)
+    _, d32 = ops.feature_forward(z, C, LO, HI, G, "relu_sq", 1.0, delta_f32=True)
+    util.assert_parity("delta f32", d32[idx], d_ref, torch.bfloat16, bias=True)
+    ops.check_status(z.device)
+
+
+def test_backward_properties_and_parity(data):
+    z, C, go = data
+    dz, dC, dC_cast = ops.feature_backward(z, C, go, LO, HI, G, "relu_sq", 0.5)
+    dz_b, dC_b, _ = ops.feature_backward(z, C, go, LO, HI, G, "relu_sq", 0.5)
+    assert torch.equal(dz, dz_b) and torch.equal(dC, dC_b)            # bitwise determinism
+    assert torch.count_nonzero(dC[:, -1, :]) == 0                     # last knot row never gets weight
+    assert torch.equal(dC_cast, dC.to(torch.bfloat16))
+    # dC against the oracle on all tokens (float64 accumulate), dz on a token subset
+    go32 = util.f32(go)
+    dz_ref_unused, dC_ref = util.oc.feature_backward(util.f32(z), util.f32(C), go32[:, H:], None, LO, HI, G,
+                                                     "identity", 0.5)
+    util.assert_parity("dC", dC, dC_ref, torch.bfloat16, bias=True)
+    idx = torch.randperm(N, generator=torch.Generator().manual_seed(2))[:512].cuda()
+    dz_ref, _ = util.oracle_backward(z[idx].contiguous(), C, go[idx].contiguous(), LO, HI, G, "relu_sq", 0.5)
+    util.assert_parity("dz", dz[idx], dz_ref, torch.bfloat16)
+    # dC is linear in the upstream gradient: doubling it doubles dC exactly
+    _, dC2, _ = ops.feature_backward(z, C, go * 2, LO, HI, G, "relu_sq", 0.5, need_dz=False)
+    assert torch.equal(dC2, 2 * dC)
+    ops.check_status(z.device)
