@@ -139,6 +139,7 @@ struct DzParams {
   int act;
   float coef;                // lambda * scale
   int chunks_total, chunks_per_split;
+  int tstages;               // depth of the transformed-table ring (2..kTStages)
   int32_t* status;
 #ifdef SKV_TC_PROFILE
   long long* prof;
@@ -214,7 +215,8 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
   constexpr uint32_t ncols = (uint32_t)(kChunkKeys * LP);            // S columns per group
   uint8_t* g_base = smem;                                             // [group][g_bytes]
   uint8_t* t_base = smem + (size_t)GROUPS * g_bytes;                  // [kTStages][t_bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(t_base + (size_t)kTStages * t_bytes);
+  const int TS = P.tstages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(t_base + (size_t)TS * t_bytes);
   uint64_t* gfull = bars;                    // [1]
   uint64_t* tfull = gfull + 1;               // [kTStages]
   uint64_t* tempty = tfull + kTStages;       // [kTStages]
@@ -330,9 +332,9 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       const uint32_t rb = (uint32_t)(r / 8) * 128u;          // bytes between 8-row groups of the T image
       const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
       for (int ci = 0; ci < nch; ++ci) {
-        const int s = ci % kTStages;
+        const int s = ci % TS;
         SKV_T(m0);
-        mbar_wait(tfull + s, (uint32_t)(ci / kTStages) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        mbar_wait(tfull + s, (uint32_t)(ci / TS) & 1u, abort_flag, P.status, kStatusTimeoutDz);
         SKV_T(m1);
         SKV_ACC(mt, m1 - m0);
         const uint32_t b_addr = smem_u32(t_base + (size_t)s * t_bytes);
@@ -376,9 +378,9 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
                  gfull);
       const uint8_t* src = reinterpret_cast<const uint8_t*>(P.timg) + (size_t)chunk_begin * t_bytes;
       for (int ci = 0; ci < nch; ++ci) {
-        const int s = ci % kTStages;
-        if (ci >= kTStages)
-          mbar_wait(tempty + s, (uint32_t)((ci / kTStages) - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        const int s = ci % TS;
+        if (ci >= TS)
+          mbar_wait(tempty + s, (uint32_t)((ci / TS) - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(tfull + s, t_bytes);
         bulk_g2s(t_base + (size_t)s * t_bytes, src + (size_t)ci * t_bytes, t_bytes, tfull + s);
@@ -627,7 +629,7 @@ __global__ void tc_dc_reduce_kernel(const float* __restrict__ part, int splits, 
 }
 
 // ------------------------------------------------------------------------------------------------
-struct DzPlan { int groups, lb, splits, chunks_per_split; size_t smem; };
+struct DzPlan { int groups, lb, splits, chunks_per_split, tstages; size_t smem; };
 
 bool plan_dz(const skv_problem& p, DzPlan* o) {
   const int lb = (p.L - 1 + 7) / 8;                  // 8-column blocks per key; columns L-1.. are padding
@@ -636,7 +638,11 @@ bool plan_dz(const skv_problem& p, DzPlan* o) {
   const int groups = 2 * ncols <= 512 ? 2 : 1;
   o->groups = groups;
   o->lb = lb;
-  o->smem = (size_t)groups * 128 * p.r * 2 + (size_t)kTStages * kChunkKeys * 8 * lb * p.r * 2 + 256;
+  int tstages = kTStages;
+  auto smem_for = [&](int ts) { return (size_t)groups * 128 * p.r * 2 + (size_t)ts * kChunkKeys * 8 * lb * p.r * 2 + 256; };
+  while (tstages > 2 && smem_for(tstages) > kSmemMax) --tstages;
+  o->tstages = tstages;
+  o->smem = smem_for(tstages);
   if (o->smem > kSmemMax) return false;
   const int chunks = p.h / kChunkKeys;
   const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
@@ -765,6 +771,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.coef = p.lambda_scale * c.g.scale;
     P.chunks_total = p.h / kChunkKeys;
     P.chunks_per_split = zp.chunks_per_split;
+    P.tstages = zp.tstages;
     P.status = c.status;
 #ifdef SKV_TC_PROFILE
     P.prof = g_prof_bwd;

@@ -25,6 +25,10 @@ SHAPES = [
     (130, 40, 64, 22),
     (96, 24, 128, 42),       # widest code dimension, G = 40
     (1, 8, 16, 22),          # a single token
+    (600, 64, 128, 22),      # rank sweep of the d20 width: r = 128, 64, 16 and G = 40
+    (520, 64, 64, 22),
+    (260, 64, 16, 22),
+    (300, 64, 32, 42),
 ]
 DTYPES = [torch.float32, torch.bfloat16]
 IMPLS = ["simt", "tcgen05"]
