@@ -486,12 +486,19 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
       const int64_t n = (tile_begin + ti) * 128 + t;
       const bool valid = n < P.N;
       const __nv_bfloat16* zrow = P.z + (valid ? n : 0) * P.zs + key0;
+      // pre-activations of the chunk after this one are requested before this one is processed
+      uint4 znext[KCH / 8];
+#pragma unroll
+      for (int i = 0; i < KCH / 8; ++i)
+        znext[i] = valid && key0 + i * 8 < P.h ? __ldg(reinterpret_cast<const uint4*>(zrow + i * 8)) : make_uint4(0, 0, 0, 0);
       for (int ch = 0; ch < nchunks; ++ch, ++use) {
         uint4 zq[KCH / 8];
 #pragma unroll
         for (int i = 0; i < KCH / 8; ++i) {
-          const bool in_h = key0 + ch * KCH + i * 8 < P.h;
-          zq[i] = valid && in_h ? __ldg(reinterpret_cast<const uint4*>(zrow + ch * KCH + i * 8)) : make_uint4(0, 0, 0, 0);
+          zq[i] = znext[i];
+          const bool in_h = ch + 1 < nchunks && key0 + (ch + 1) * KCH + i * 8 < P.h;
+          znext[i] = valid && in_h ? __ldg(reinterpret_cast<const uint4*>(zrow + (ch + 1) * KCH + i * 8))
+                                   : make_uint4(0, 0, 0, 0);
         }
         if (use > 0) mbar_wait(pempty + pg, (uint32_t)(use - 1) & 1u, abort_flag, P.status, kStatusTimeoutDc);
         if (have_saved) {

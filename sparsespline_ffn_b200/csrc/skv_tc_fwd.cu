@@ -21,6 +21,8 @@
 //
 // Every mbarrier wait is bounded (skv_tc_common.cuh); a timed-out wait sets the status word and
 // lets the CTA drain.
+#include <cstdlib>
+
 #include "skv_tc_common.cuh"
 
 namespace skv {
@@ -49,6 +51,7 @@ struct FwdParams {
   int32_t* status;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   int cstages;              // depth of the code-table ring (2..4)
+  int stagger_cycles;       // start offset between token groups (tensor-memory variant)
 #ifdef SKV_TC_PROFILE
   long long* prof;          // [ctas][8] phase cycle counters (diagnostic builds only)
 #endif
@@ -342,6 +345,14 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
     const bool relu = P.act == SKV_ACT_RELU_SQ;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
+    // Stagger the token groups by a fraction of a chunk period: a group that is waiting for its
+    // MMAs then leaves its issue slots to groups that are building, instead of all groups
+    // building and waiting in lockstep.
+    {
+      const long long t0 = clock64();
+      const long long delay = (long long)grp * P.stagger_cycles;
+      while (clock64() - t0 < delay) {}
+    }
 
 #ifdef SKV_TC_PROFILE
     long long pw = 0, pb = 0, pf = 0;
@@ -639,6 +650,7 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.chunks_per_split = f.chunks_per_split;
   P.status = c.status;
   P.cstages = f.cstages;
+  P.stagger_cycles = getenv("SKV_STAGGER") ? atoi(getenv("SKV_STAGGER")) : 700;
 #ifdef SKV_TC_PROFILE
   P.prof = g_prof;
 #endif
