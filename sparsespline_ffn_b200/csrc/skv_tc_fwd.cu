@@ -21,8 +21,6 @@
 //
 // Every mbarrier wait is bounded (skv_tc_common.cuh); a timed-out wait sets the status word and
 // lets the CTA drain.
-#include <cstdlib>
-
 #include "skv_tc_common.cuh"
 
 namespace skv {
@@ -51,7 +49,6 @@ struct FwdParams {
   int32_t* status;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   int cstages;              // depth of the code-table ring (2..4)
-  int stagger_cycles;       // start offset between token groups (tensor-memory variant)
 #ifdef SKV_TC_PROFILE
   long long* prof;          // [ctas][8] phase cycle counters (diagnostic builds only)
 #endif
@@ -126,8 +123,10 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
     long long pw = 0, pb = 0, pf = 0;
     const long long pstart = clock64();
 #define SKV_T(x) const long long x = clock64()
+#define SKV_ACC(a, expr) a += (expr)
 #else
 #define SKV_T(x)
+#define SKV_ACC(a, expr)
 #endif
     auto chunk_body = [&](int ci, int s, uint32_t(&sv)[kChunkKeys]) {
       SKV_T(c0);
@@ -300,15 +299,20 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 template <int GROUPS, int HL>
 __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(const FwdParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int L = 2 * HL, r = P.r;
-  const uint32_t c_bytes = (uint32_t)(kChunkKeys * L * r * 2);
+  // Keys are padded to HLP words (an even count), so that half a chunk (4 keys) is a whole number
+  // of K = 16 steps; the code-table image has 2*HLP rows per key, the padding rows are zero.
+  constexpr int HLP = (HL + 1) & ~1;
+  constexpr int kHalfKeys = kChunkKeys / 2;
+  constexpr int kHalfSteps = kHalfKeys * HLP / 8;                  // K = 16 steps per half chunk
+  const int r = P.r;
+  const uint32_t c_bytes = (uint32_t)(kChunkKeys * 2 * HLP * r * 2);
   const int CS = P.cstages;
   uint8_t* c_base = smem;                                          // [cstage][c_bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(c_base + (size_t)CS * c_bytes);
-  uint64_t* full = bars;                          // [group]    producers -> MMA
-  uint64_t* empty = full + GROUPS;                // [group]    MMA -> producers
-  uint64_t* cfull = empty + GROUPS;               // [cstage]   TMA -> MMA
-  uint64_t* cempty = cfull + kMaxTaCStages;       // [cstage]   MMA -> TMA
+  uint64_t* full = bars;                          // [group][half]  producers -> MMA
+  uint64_t* empty = full + 2 * GROUPS;            // [group][half]  MMA -> producers
+  uint64_t* cfull = empty + 2 * GROUPS;           // [cstage]       TMA -> MMA
+  uint64_t* cempty = cfull + kMaxTaCStages;       // [cstage]       MMA -> TMA
   uint64_t* done = cempty + kMaxTaCStages;        // [group]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + GROUPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -317,12 +321,13 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   const int chunk_begin = blockIdx.y * P.chunks_per_split;
   const int nch = min(P.chunks_per_split, P.chunks_total - chunk_begin);
   const int64_t tile_base = (int64_t)blockIdx.x * (128 * GROUPS);
-  const uint32_t grp_cols = (uint32_t)(kChunkKeys * HL + r);
+  const uint32_t grp_cols = (uint32_t)(kChunkKeys * HLP + r);
   uint32_t tmem_cols = 32;
   while (tmem_cols < GROUPS * grp_cols) tmem_cols <<= 1;
 
   if (tid == 0) {
-    for (int i = 0; i < GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); mbar_init(done + i, 1); }
+    for (int i = 0; i < 2 * GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); }
+    for (int i = 0; i < GROUPS; ++i) mbar_init(done + i, 1);
     for (int i = 0; i < kMaxTaCStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, GROUPS); }
     *abort_flag = 0;
     mbar_init_fence();
@@ -345,57 +350,55 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
     const bool relu = P.act == SKV_ACT_RELU_SQ;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
-    // Stagger the token groups by a fraction of a chunk period: a group that is waiting for its
-    // MMAs then leaves its issue slots to groups that are building, instead of all groups
-    // building and waiting in lockstep.
-    {
-      const long long t0 = clock64();
-      const long long delay = (long long)grp * P.stagger_cycles;
-      while (clock64() - t0 < delay) {}
-    }
-
 #ifdef SKV_TC_PROFILE
     long long pw = 0, pb = 0, pf = 0;
     const long long pstart = clock64();
 #endif
     for (int ci = 0; ci < nch; ++ci) {
-      SKV_T(c0);
       const uint4 zc = znext;
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
       const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
       uint32_t aw[4];
-      if (ci > 0) {
-        mbar_wait(empty + grp, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
-        tc_fence_after();
-      }
-      SKV_T(c1);
+      // The group's A columns are written and consumed in two halves of 4 keys: the MMAs of one
+      // half run while the other half is being built, so the producers do not wait for them.
 #pragma unroll
-      for (int q = 0; q < kChunkKeys; ++q) {
-        const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
-        uint32_t x0, x1, wp;
-        phi_pair_words(valid ? zz : __int_as_float(0x7fc00000), P.g, x0, x1, wp);   // NaN row: all weights zero
-        uint32_t W[HL];
-        W[0] = wp == 0u ? x0 : 0u;
+      for (int half = 0; half < 2; ++half) {
+        SKV_T(c0);
+        if (ci > 0) {
+          mbar_wait(empty + grp * 2 + half, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+          tc_fence_after();
+        }
+        SKV_T(c1);
 #pragma unroll
-        for (int i = 1; i < HL - 1; ++i) W[i] = wp == (uint32_t)i ? x0 : (wp == (uint32_t)(i - 1) ? x1 : 0u);
-        W[HL - 1] = wp == (uint32_t)(HL - 2) ? x1 : 0u;
-        tmem_st_words<HL>(lane_addr + (uint32_t)(q * HL), W);
-        const float zp = fmaxf(zz, 0.0f);
-        const float a = relu ? zp * zp : zz;
-        if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
-        else aw[q >> 1] = __float_as_uint(a);
-      }
-      SKV_T(c2);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(full + grp);
+        for (int qq = 0; qq < kHalfKeys; ++qq) {
+          const int q = half * kHalfKeys + qq;
+          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+          uint32_t x0, x1, wp;
+          phi_pair_words(valid ? zz : __int_as_float(0x7fc00000), P.g, x0, x1, wp);   // NaN row: all weights zero
+          uint32_t W[HLP];
+          W[0] = wp == 0u ? x0 : 0u;
+#pragma unroll
+          for (int i = 1; i < HL - 1; ++i) W[i] = wp == (uint32_t)i ? x0 : (wp == (uint32_t)(i - 1) ? x1 : 0u);
+          W[HL - 1] = wp == (uint32_t)(HL - 2) ? x1 : 0u;
+#pragma unroll
+          for (int i = HL; i < HLP; ++i) W[i] = 0u;
+          tmem_st_words<HLP>(lane_addr + (uint32_t)(q * HLP), W);
+          const float zp = fmaxf(zz, 0.0f);
+          const float a = relu ? zp * zp : zz;
+          if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
+          else aw[q >> 1] = __float_as_uint(a);
+        }
+        SKV_T(c2);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(full + grp * 2 + half);
 #ifdef SKV_TC_PROFILE
-      const long long c3 = clock64();
-      pw += c1 - c0; pb += c2 - c1; pf += c3 - c2;
+        const long long c3 = clock64();
+        pw += c1 - c0; pb += c2 - c1; pf += c3 - c2;
 #endif
+      }
       if (arow && valid) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
     }
-
 #ifdef SKV_TC_PROFILE
     if (tid == 0) {
       long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
@@ -406,7 +409,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     mbar_wait(done + grp, 0, abort_flag, P.status, kStatusTimeoutFwd);
     tc_fence_after();
     float* prow = P.partial + ((size_t)blockIdx.y * P.N + (valid ? n : 0)) * r;
-    const uint32_t daddr = lane_addr + (uint32_t)(kChunkKeys * HL);
+    const uint32_t daddr = lane_addr + (uint32_t)(kChunkKeys * HLP);
     for (int c0 = 0; c0 < r; c0 += 16) {
       float v[16];
       tmem_ld16(daddr + c0, v);
@@ -419,14 +422,14 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     tc_fence_before();
   } else if (warp < 5 * GROUPS) {
     // ------------------------------------------------------------------ MMA issue, one warp per token group
-    // (a single issuing thread for all groups is starved of issue slots by the producer warps)
+    // (one thread cannot issue N = r MMAs faster than about one per 45 cycles)
     if (lane == 0) {
       const int grp = warp - 4 * GROUPS;
       const uint32_t idesc = instr_desc(0, 0, 0, 1, 128, r);
       const uint32_t b_hi = desc_hi(P.b_sbo);
       const uint32_t b_step = (2u * (uint32_t)(r / 8) * 128u) >> 4;          // per K=16 step
       const uint32_t a_addr0 = tmem_base + (uint32_t)grp * grp_cols;
-      const uint32_t d_addr = a_addr0 + (uint32_t)(kChunkKeys * HL);
+      const uint32_t d_addr = a_addr0 + (uint32_t)(kChunkKeys * HLP);
 #ifdef SKV_TC_PROFILE
       long long mc = 0, mf = 0, mi = 0;
       const long long mstart = clock64();
@@ -436,24 +439,27 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
         SKV_T(m0);
         mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
         SKV_T(m1);
-        mbar_wait(full + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutFwd);
-        SKV_T(m3);
-        tc_fence_after();
-        uint32_t a_addr = a_addr0;
+        SKV_ACC(mc, m1 - m0);
         uint32_t b_lo = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
-        umma_f16_ta(d_addr, a_addr, b_lo, b_hi, idesc, ci > 0 ? 1u : 0u);
+        uint32_t a_addr = a_addr0;
 #pragma unroll
-        for (int ks = 1; ks < HL; ++ks) {            // 8*L/16 = HL steps of K = 16 (8 columns of A each)
-          a_addr += 8u;
-          b_lo += b_step;
-          umma_f16_ta(d_addr, a_addr, b_lo, b_hi, idesc, 1u);
+        for (int half = 0; half < 2; ++half) {
+          SKV_T(m2);
+          mbar_wait(full + grp * 2 + half, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+          SKV_T(m3);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kHalfSteps; ++ks) {     // 8 columns of A (16 K elements) per step
+            umma_f16_ta(d_addr, a_addr, b_lo, b_hi, idesc, (ci > 0 || half > 0 || ks > 0) ? 1u : 0u);
+            a_addr += 8u;
+            b_lo += b_step;
+          }
+          umma_commit(empty + grp * 2 + half);
+          SKV_T(m4);
+          SKV_ACC(mf, m3 - m2);
+          SKV_ACC(mi, m4 - m3);
         }
-        umma_commit(empty + grp);
         umma_commit(cempty + cs);
-#ifdef SKV_TC_PROFILE
-        const long long m4 = clock64();
-        mc += m1 - m0; mf += m3 - m1; mi += m4 - m3;
-#endif
       }
       umma_commit(done + grp);
 #ifdef SKV_TC_PROFILE
@@ -491,16 +497,19 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
 
 // C [h][L][r] bf16 -> f16 image: per 8-key chunk the [8L x r] tile as 8x8 core matrices,
 // core (kg, cg) at ((kg * r/8 + cg) * 128) bytes, row k%8 at 16 bytes, channel c%8 at 2 bytes.
-__global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int r) {
-  const int rows_per_chunk = kChunkKeys * L;
+__global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int LP,
+                                 int r) {
+  const int rows_per_chunk = kChunkKeys * LP;          // LP >= L rows per key in the image, rows L.. are zero
   const int cgs = r / 8;
-  const size_t pieces = (size_t)h * L * cgs;
+  const size_t pieces = (size_t)h * LP * cgs;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (size_t)gridDim.x * blockDim.x) {
     const int cg = (int)(i % cgs);
-    const size_t rowg = i / cgs;                       // global (j, b) row
+    const size_t rowg = i / cgs;                       // (j, b) row of the padded image
     const int chunk = (int)(rowg / rows_per_chunk);
     const int k = (int)(rowg % rows_per_chunk);
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(C + rowg * r + cg * 8));
+    const int j = (int)(rowg / LP), bb = (int)(rowg % LP);
+    const uint4 v = bb < L ? __ldg(reinterpret_cast<const uint4*>(C + ((size_t)j * L + bb) * r + cg * 8))
+                           : make_uint4(0, 0, 0, 0);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[4];
 #pragma unroll
@@ -543,17 +552,18 @@ size_t fwd_smem(int groups, int cstages, int L, int r) {
 bool plan_forward(const skv_problem& p, FwdPlan* out) {
   out->ta = false;
   const int hl = p.L / 2;
-  if (p.L % 2 == 0 && ta_supported_hl(hl) && kChunkKeys * hl + p.r <= 512) {
-    int groups = 512 / (kChunkKeys * hl + p.r);
+  const int hlp = (hl + 1) & ~1;                      // words per key in tensor memory (padded to even)
+  if (p.L % 2 == 0 && ta_supported_hl(hl) && kChunkKeys * hlp + p.r <= 512) {
+    int groups = 512 / (kChunkKeys * hlp + p.r);
     if (groups > 4) groups = 4;
-    const size_t c_bytes = (size_t)kChunkKeys * p.L * p.r * 2;
-    int cstages = (int)((kSmemLimit - 256) / c_bytes);
+    const size_t c_bytes = (size_t)kChunkKeys * 2 * hlp * p.r * 2;
+    int cstages = (int)((kSmemLimit - 512) / c_bytes);
     if (cstages > kMaxTaCStages) cstages = kMaxTaCStages;
     if (cstages >= 2) {
       out->ta = true;
       out->groups = groups;
       out->cstages = cstages;
-      out->smem = (size_t)cstages * c_bytes + 256;
+      out->smem = (size_t)cstages * c_bytes + 512;       // ring + barriers
       const int chunks = p.h / kChunkKeys;
       const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
       int best = 1;
@@ -607,7 +617,8 @@ bool fwd_eligible(const skv_problem& p) {
   return plan_forward(p, &f);
 }
 
-size_t cimg_bytes(const skv_problem& p) { return align256((size_t)p.h * p.L * p.r * sizeof(__half)); }
+// sized for the padded image of the tensor-memory variant (L rounded up to a multiple of 4 rows per key)
+size_t cimg_bytes(const skv_problem& p) { return align256((size_t)p.h * ((p.L + 3) / 4 * 4) * p.r * sizeof(__half)); }
 
 size_t fwd_scratch_bytes(const skv_problem& p) {
   FwdPlan f;
@@ -615,10 +626,10 @@ size_t fwd_scratch_bytes(const skv_problem& p) {
   return cimg_bytes(p) + align256((size_t)f.splits * (p.N > 0 ? p.N : 1) * p.r * sizeof(float));
 }
 
-int launch_pack_c(const LaunchCtx& c, const void* C, void* img) {
-  const size_t pieces = (size_t)c.p.h * c.p.L * (c.p.r / 8);
+int launch_pack_c(const LaunchCtx& c, const void* C, void* img, int LP) {
+  const size_t pieces = (size_t)c.p.h * LP * (c.p.r / 8);
   const unsigned grid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
-  tc_pack_c_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, (__half*)img, c.p.h, c.p.L, c.p.r);
+  tc_pack_c_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, (__half*)img, c.p.h, c.p.L, LP, c.p.r);
   note_launches(1);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_LAUNCH;
 }
@@ -631,7 +642,7 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   if (scratch_bytes < fwd_scratch_bytes(p)) return SKV_ERR_SCRATCH;
   __half* img = reinterpret_cast<__half*>(scratch);
   float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + cimg_bytes(p));
-  if (int e = launch_pack_c(c, C, img)) return e;
+  if (int e = launch_pack_c(c, C, img, f.ta ? ((p.L / 2 + 1) & ~1) * 2 : p.L)) return e;
 
   FwdParams P;
   P.z = (const __nv_bfloat16*)z;
@@ -650,7 +661,6 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.chunks_per_split = f.chunks_per_split;
   P.status = c.status;
   P.cstages = f.cstages;
-  P.stagger_cycles = getenv("SKV_STAGGER") ? atoi(getenv("SKV_STAGGER")) : 700;
 #ifdef SKV_TC_PROFILE
   P.prof = g_prof;
 #endif
