@@ -198,7 +198,7 @@ __device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t
   const Knot k = knot_of(zz, g);
   const float t = k.tau, omt = 1.0f - t;
   const float m = k.in_range ? 1.0f : 0.0f;
-  const float hm = k.in_range ? 0.5f : 0.0f;
+  const float hm = 0.5f * m;
   const float B0 = (hm * omt) * omt;
   const float B2 = (hm * t) * t;
   const float B1 = (m - B0) - B2;
@@ -218,7 +218,7 @@ __device__ __forceinline__ void phi_pair_words(float zz, const GridParams& g, ui
   const Knot k = knot_of(zz, g);
   const float t = k.tau, omt = 1.0f - t;
   const float m = k.in_range ? 1.0f : 0.0f;
-  const float hm = k.in_range ? 0.5f : 0.0f;
+  const float hm = 0.5f * m;
   const float B0 = (hm * omt) * omt;
   const float B2 = (hm * t) * t;
   const float B1 = (m - B0) - B2;

@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 // accumulator; with four groups (512 tokens per CTA, 16 producer warps) the other groups keep the
 // SM busy while one group waits for its MMAs.
 // ---------------------------------------------------------------------------------------------
-template <int GROUPS, int HL>
+template <int GROUPS, int HL, bool RELU>
 __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(const FwdParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // Keys are padded to HLP words (an even count), so that half a chunk (4 keys) is a whole number
@@ -348,7 +348,6 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     const __nv_bfloat16* zrow = P.z + (valid ? n : 0) * P.zs + (int64_t)chunk_begin * kChunkKeys;
     __nv_bfloat16* arow = P.act_out ? P.act_out + (valid ? n : 0) * P.as + (int64_t)chunk_begin * kChunkKeys : nullptr;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
-    const bool relu = P.act == SKV_ACT_RELU_SQ;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
 #ifdef SKV_TC_PROFILE
     long long pw = 0, pb = 0, pf = 0;
@@ -374,7 +373,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           const int q = half * kHalfKeys + qq;
           const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
           uint32_t x0, x1, wp;
-          phi_pair_words(valid ? zz : __int_as_float(0x7fc00000), P.g, x0, x1, wp);   // NaN row: all weights zero
+          phi_pair_words(zz, P.g, x0, x1, wp);   // rows past N read z = 0; their accumulator rows are never stored
           uint32_t W[HLP];
           W[0] = wp == 0u ? x0 : 0u;
 #pragma unroll
@@ -384,7 +383,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           for (int i = HL; i < HLP; ++i) W[i] = 0u;
           tmem_st_words<HLP>(lane_addr + (uint32_t)(q * HLP), W);
           const float zp = fmaxf(zz, 0.0f);
-          const float a = relu ? zp * zp : zz;
+          const float a = RELU ? zp * zp : zz;
           if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
           else aw[q >> 1] = __float_as_uint(a);
         }
@@ -679,8 +678,15 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
     const int hl = p.L / 2;
 #define SKV_TA_CASE(G_, HL_)                                                                                         \
   if (f.groups == G_ && hl == HL_) {                                                                                 \
-    err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem); \
-    if (err == cudaSuccess) tc_forward_ta_kernel<G_, HL_><<<grid, threads, f.smem, c.stream>>>(P);                   \
+    if (p.activation == SKV_ACT_RELU_SQ) {                                                                           \
+      err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 (int)f.smem);                                                                       \
+      if (err == cudaSuccess) tc_forward_ta_kernel<G_, HL_, true><<<grid, threads, f.smem, c.stream>>>(P);           \
+    } else {                                                                                                         \
+      err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                 (int)f.smem);                                                                       \
+      if (err == cudaSuccess) tc_forward_ta_kernel<G_, HL_, false><<<grid, threads, f.smem, c.stream>>>(P);          \
+    }                                                                                                                \
   }
     SKV_TA_CASE(1, 8) SKV_TA_CASE(2, 8) SKV_TA_CASE(3, 8) SKV_TA_CASE(4, 8)
     SKV_TA_CASE(1, 11) SKV_TA_CASE(2, 11) SKV_TA_CASE(3, 11) SKV_TA_CASE(4, 11)
