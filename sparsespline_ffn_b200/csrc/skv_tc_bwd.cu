@@ -418,8 +418,6 @@ struct DcParams {
   int32_t* status;
 };
 
-__device__ __forceinline__ uint32_t word_off(uint32_t w) { return (w >> 2) * 2048u + (w & 3u) * 4u; }
-
 // KCH = keys per chunk.  Two producer groups of 128 threads (thread = token of the group's tile).
 template <int KCH>
 __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {

@@ -54,8 +54,6 @@ struct FwdParams {
 #endif
 };
 
-__device__ __forceinline__ uint32_t word_off(uint32_t w) { return (w >> 2) * 2048u + (w & 3u) * 4u; }
-
 template <int GROUPS>
 __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const FwdParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
