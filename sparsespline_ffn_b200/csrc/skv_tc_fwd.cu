@@ -49,6 +49,7 @@ struct FwdParams {
   int32_t* status;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   int cstages;              // depth of the code-table ring (2..4)
+  int nstaged;              // keys per chunk placed through the shared-memory staging row (0..8)
 #ifdef SKV_TC_PROFILE
   long long* prof;          // [ctas][8] phase cycle counters (diagnostic builds only)
 #endif
@@ -306,7 +307,15 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   const uint32_t c_bytes = (uint32_t)(kChunkKeys * 2 * HLP * r * 2);
   const int CS = P.cstages;
   uint8_t* c_base = smem;                                          // [cstage][c_bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(c_base + (size_t)CS * c_bytes);
+  // One private staging row of SW words per producer thread.  Placing the two non-zero words of a
+  // row segment costs about thirty compare/select instructions on the half-rate ALU pipe; for
+  // the first P.nstaged keys of every chunk the thread instead stores the two words into its
+  // (zeroed) staging row at the dynamic position, reads the row back with three 16-byte loads and
+  // zeroes the two words again, which moves that work to the load/store pipe.  SW/4 is odd, so
+  // the rows of eight consecutive threads start in eight different bank quads.
+  constexpr int SW = (HLP % 8 == 4) ? HLP : (HLP + 7) / 8 * 8 + 4;
+  uint8_t* stage_base = c_base + (size_t)CS * c_bytes;             // [128*GROUPS][SW words]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_base + (size_t)128 * GROUPS * SW * 4);
   uint64_t* full = bars;                          // [group][half]  producers -> MMA
   uint64_t* empty = full + 2 * GROUPS;            // [group][half]  MMA -> producers
   uint64_t* cfull = empty + 2 * GROUPS;           // [cstage]       TMA -> MMA
@@ -330,6 +339,8 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     *abort_flag = 0;
     mbar_init_fence();
   }
+  for (uint32_t i = tid; i < (uint32_t)(128 * GROUPS * SW / 4); i += blockDim.x)
+    reinterpret_cast<uint4*>(stage_base)[i] = make_uint4(0, 0, 0, 0);
   if (warp == 5 * GROUPS) tmem_alloc(tmem_slot, tmem_cols);
   fence_async_smem();
   tc_fence_before();
@@ -347,6 +358,8 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     __nv_bfloat16* arow = P.act_out ? P.act_out + (valid ? n : 0) * P.as + (int64_t)chunk_begin * kChunkKeys : nullptr;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
+    const uint32_t srow = smem_u32(stage_base) + (uint32_t)(tid * SW * 4);
+    const int nstaged = P.nstaged;
 #ifdef SKV_TC_PROFILE
     long long pw = 0, pb = 0, pf = 0;
     const long long pstart = clock64();
@@ -373,12 +386,34 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           uint32_t x0, x1, wp;
           phi_pair_words(zz, P.g, x0, x1, wp);   // rows past N read z = 0; their accumulator rows are never stored
           uint32_t W[HLP];
-          W[0] = wp == 0u ? x0 : 0u;
+          if (q < nstaged) {
+            const uint32_t pos = srow + wp * 4u;
+            sts32(pos, x0);
+            sts32(pos + 4u, x1);
 #pragma unroll
-          for (int i = 1; i < HL - 1; ++i) W[i] = wp == (uint32_t)i ? x0 : (wp == (uint32_t)(i - 1) ? x1 : 0u);
-          W[HL - 1] = wp == (uint32_t)(HL - 2) ? x1 : 0u;
+            for (int i = 0; i < HLP; i += 4) {
+              if (i + 4 <= HLP) {
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(W[i]), "=r"(W[i + 1]), "=r"(W[i + 2]), "=r"(W[i + 3])
+                             : "r"(srow + (uint32_t)i * 4u)
+                             : "memory");
+              } else {
+                asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];"
+                             : "=r"(W[i]), "=r"(W[i + 1])
+                             : "r"(srow + (uint32_t)i * 4u)
+                             : "memory");
+              }
+            }
+            sts32(pos, 0u);
+            sts32(pos + 4u, 0u);
+          } else {
+            W[0] = wp == 0u ? x0 : 0u;
 #pragma unroll
-          for (int i = HL; i < HLP; ++i) W[i] = 0u;
+            for (int i = 1; i < HL - 1; ++i) W[i] = wp == (uint32_t)i ? x0 : (wp == (uint32_t)(i - 1) ? x1 : 0u);
+            W[HL - 1] = wp == (uint32_t)(HL - 2) ? x1 : 0u;
+#pragma unroll
+            for (int i = HL; i < HLP; ++i) W[i] = 0u;
+          }
           tmem_st_words<HLP>(lane_addr + (uint32_t)(q * HLP), W);
           const float zp = fmaxf(zz, 0.0f);
           const float a = RELU ? zp * zp : zz;
@@ -554,13 +589,15 @@ bool plan_forward(const skv_problem& p, FwdPlan* out) {
     int groups = 512 / (kChunkKeys * hlp + p.r);
     if (groups > 4) groups = 4;
     const size_t c_bytes = (size_t)kChunkKeys * 2 * hlp * p.r * 2;
-    int cstages = (int)((kSmemLimit - 512) / c_bytes);
+    const int sw = (hlp % 8 == 4) ? hlp : (hlp + 7) / 8 * 8 + 4;      // staging-row words per producer thread
+    const size_t stage_bytes = (size_t)128 * groups * sw * 4;
+    int cstages = (int)((kSmemLimit - 512 - stage_bytes) / c_bytes);
     if (cstages > kMaxTaCStages) cstages = kMaxTaCStages;
     if (cstages >= 2) {
       out->ta = true;
       out->groups = groups;
       out->cstages = cstages;
-      out->smem = (size_t)cstages * c_bytes + 512;       // ring + barriers
+      out->smem = (size_t)cstages * c_bytes + stage_bytes + 512;       // ring + staging rows + barriers
       const int chunks = p.h / kChunkKeys;
       const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
       int best = 1;
@@ -658,6 +695,7 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.chunks_per_split = f.chunks_per_split;
   P.status = c.status;
   P.cstages = f.cstages;
+  P.nstaged = 4;            // measured best at the d20 shape (3..5 within 1 %)
 #ifdef SKV_TC_PROFILE
   P.prof = g_prof;
 #endif
