@@ -10,7 +10,8 @@ pre-activations, with the float32 dC all-reduce over NCCL).  Rank 0 prints one J
 
 * ``value``: tokens/s of all ranks with inputs resident in HBM, CUDA-event timed, max over ranks.
 * ``e2e``: the same through the public operator with HOST buffers: each step copies z and the
-  upstream gradient from pinned host memory and copies f, dz and dC back.
+  upstream gradient from pinned host memory and copies f, dz and dC back, pipelined over eight
+  token chunks on three streams so that copies in both directions overlap the kernels.
 * ``roofline``: the slowest of the three main kernels (forward, dz, dC), timed alone with CUDA
   events in a separate pass of the same length, against the measured dense bf16 peak.
 * ``cpu_baseline``: the CPU oracle (a C/OpenMP port of the reference's algorithm) on a bounded
@@ -320,21 +321,55 @@ def main():
         zdev = torch.empty_like(zh, device=dev)
         godev = torch.empty_like(goh, device=dev)
 
+        # The step is pipelined over NCH token chunks on three streams: the host-to-device copies of
+        # chunk i+1, the operator's forward+backward on chunk i and the device-to-host copies of chunk
+        # i-1 overlap (PCIe is full duplex); dC is accumulated across the chunks on the device, as
+        # autograd does for micro-batches, and copied back once.
+        NCH = 8 if N % 8 == 0 and N >= 8192 else 1
+        rows = N // NCH
+        s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        state = dict(prev_comp=[None] * NCH)
+
         def step_e2e():
-            zdev.copy_(zh, non_blocking=True)
-            godev.copy_(goh, non_blocking=True)
-            zz = zdev.requires_grad_(True)
-            zz.grad = None
+            cur = torch.cuda.current_stream()
+            s_in.wait_stream(cur)
+            s_comp.wait_stream(cur)
+            s_out.wait_stream(cur)
             C.grad = None
-            if world == 1:
-                f = flash_spline_feature(zz, C, lo, hi, G, "relu_sq", lam, True)
-            else:
-                f = sharded.token_sharded_spline_feature(zz, C, lo, hi, G, "relu_sq", lam)
-            f.backward(godev)
-            fh.copy_(f.detach(), non_blocking=True)
-            dzh.copy_(zz.grad, non_blocking=True)
-            dCh.copy_(C.grad, non_blocking=True)
-            zdev.requires_grad_(False)
+            keep = []
+            for c in range(NCH):
+                sl = slice(c * rows, (c + 1) * rows)
+                with torch.cuda.stream(s_in):
+                    if state["prev_comp"][c] is not None:
+                        s_in.wait_event(state["prev_comp"][c])     # chunk buffers still read by the last step
+                    zdev[sl].copy_(zh[sl], non_blocking=True)
+                    godev[sl].copy_(goh[sl], non_blocking=True)
+                    ev_in = torch.cuda.Event()
+                    ev_in.record(s_in)
+                with torch.cuda.stream(s_comp):
+                    s_comp.wait_event(ev_in)
+                    zz = zdev[sl].detach().requires_grad_(True)
+                    if world == 1:
+                        f = flash_spline_feature(zz, C, lo, hi, G, "relu_sq", lam, True)
+                    else:
+                        f = sharded.token_sharded_spline_feature(zz, C, lo, hi, G, "relu_sq", lam)
+                    f.backward(godev[sl])
+                    ev_c = torch.cuda.Event()
+                    ev_c.record(s_comp)
+                    state["prev_comp"][c] = ev_c
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_c)
+                    fh[sl].copy_(f.detach(), non_blocking=True)
+                    dzh[sl].copy_(zz.grad, non_blocking=True)
+                    f.record_stream(s_out)
+                    zz.grad.record_stream(s_out)
+                keep.append((f, zz))
+            with torch.cuda.stream(s_out):
+                s_out.wait_stream(s_comp)
+                dCh.copy_(C.grad, non_blocking=True)
+                C.grad.record_stream(s_out)
+            cur.wait_stream(s_out)
+            cur.wait_stream(s_comp)
 
         for _ in range(2):
             step_e2e()
@@ -343,7 +378,7 @@ def main():
         h2d = zh.numel() * 2 + goh.numel() * 2
         d2h = fh.numel() * 2 + dzh.numel() * 2 + dCh.numel() * 2
         e2e = dict(value=world * N / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
-                   d2h_bytes_per_step=d2h, ms_per_step=e2e_ms)
+                   d2h_bytes_per_step=d2h, ms_per_step=e2e_ms, token_chunks=NCH)
         ops.check_status(dev)
 
     cpu_baseline = None

@@ -30,9 +30,6 @@ namespace tc {
 size_t cimg_bytes(const skv_problem& p);
 bool fwd_eligible(const skv_problem& p);
 
-#ifdef SKV_TC_PROFILE
-long long* g_prof_bwd = nullptr;
-#endif
 
 namespace {
 
@@ -141,18 +138,8 @@ struct DzParams {
   int chunks_total, chunks_per_split;
   int tstages;               // depth of the transformed-table ring (2..kTStages)
   int32_t* status;
-#ifdef SKV_TC_PROFILE
-  long long* prof;
-#endif
 };
 
-#ifdef SKV_TC_PROFILE
-#define SKV_T(x) const long long x = clock64()
-#define SKV_ACC(a, expr) a += (expr)
-#else
-#define SKV_T(x)
-#define SKV_ACC(a, expr)
-#endif
 
 // Tensor-memory loads of one key's S columns (LB blocks of 8 float32 columns of this warp's lanes).
 // The loads are issued without waiting; tmem_wait_key waits for all outstanding loads and ties
@@ -264,10 +251,6 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
     uint4 ganext = valid && nch > 0 && garow ? __ldg(reinterpret_cast<const uint4*>(garow)) : make_uint4(0, 0, 0, 0);
 
-#ifdef SKV_TC_PROFILE
-    long long pw = 0, pl = 0;
-    const long long pstart = clock64();
-#endif
     for (int ci = 0; ci < nch; ++ci) {
       const uint4 zc = znext, gac = ganext;
       if (ci + 1 < nch && valid) {
@@ -278,19 +261,13 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       const uint32_t gw[4] = {gac.x, gac.y, gac.z, gac.w};
       uint32_t bufa[LB][8], bufb[LB][8];
       float outv[kChunkKeys];
-      SKV_T(k0);
       mbar_wait(sfull + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutDz);
-      SKV_T(k1);
-      SKV_ACC(pw, k1 - k0);
       tc_fence_after();
       tmem_ld_key<LB>(trow, bufa);
 #pragma unroll
       for (int q = 0; q < kChunkKeys; ++q) {
         // the loads of key q are in flight; wait, start the loads of key q+1, then do key q's math
-        SKV_T(k2);
         if (q & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
-        SKV_T(k3);
-        SKV_ACC(pl, k3 - k2);
         if (q + 1 < kChunkKeys) {
           if (q & 1) tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufa);
           else tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufb);
@@ -315,34 +292,18 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
             make_uint4(pack_bf2(outv[0], outv[1]), pack_bf2(outv[2], outv[3]), pack_bf2(outv[4], outv[5]),
                        pack_bf2(outv[6], outv[7]));
     }
-#ifdef SKV_TC_PROFILE
-    if (tid == 0) {
-      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-      o[0] = clock64() - pstart; o[1] = pw; o[2] = pl;
-    }
-#endif
   } else if (warp == 4 * GROUPS) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-#ifdef SKV_TC_PROFILE
-      long long ms = 0, mt = 0, mi = 0;
-      const long long mstart = clock64();
-#endif
       mbar_wait(gfull, 0, abort_flag, P.status, kStatusTimeoutDz);
       const uint32_t rb = (uint32_t)(r / 8) * 128u;          // bytes between 8-row groups of the T image
       const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % TS;
-        SKV_T(m0);
         mbar_wait(tfull + s, (uint32_t)(ci / TS) & 1u, abort_flag, P.status, kStatusTimeoutDz);
-        SKV_T(m1);
-        SKV_ACC(mt, m1 - m0);
         const uint32_t b_addr = smem_u32(t_base + (size_t)s * t_bytes);
         for (int grp = 0; grp < GROUPS; ++grp) {
-          SKV_T(m2);
           if (ci > 0) mbar_wait(sempty + grp, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
-          SKV_T(m3);
-          SKV_ACC(ms, m3 - m2);
           tc_fence_after();
           const uint32_t a_lo0 = desc_lo(smem_u32(g_base + (size_t)grp * g_bytes), 2048u);
           for (uint32_t c0 = 0; c0 < ncols; c0 += 256) {
@@ -358,15 +319,9 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
             }
           }
           umma_commit(sfull + grp);
-          SKV_T(m4);
-          SKV_ACC(mi, m4 - m3);
         }
         umma_commit(tempty + s);
       }
-#ifdef SKV_TC_PROFILE
-      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-      o[4] = clock64() - mstart; o[5] = mt; o[6] = ms; o[7] = mi;
-#endif
     }
   } else {
     // ------------------------------------------------------------------ loader
@@ -778,9 +733,6 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.chunks_per_split = zp.chunks_per_split;
     P.tstages = zp.tstages;
     P.status = c.status;
-#ifdef SKV_TC_PROFILE
-    P.prof = g_prof_bwd;
-#endif
     const int64_t tiles = (p.N + 128 * zp.groups - 1) / (128 * zp.groups);
     dim3 grid((unsigned)tiles, (unsigned)zp.splits);
     const unsigned threads = 128 * zp.groups + 64;

@@ -50,9 +50,6 @@ struct FwdParams {
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   int cstages;              // depth of the code-table ring (2..4)
   int nstaged;              // keys per chunk placed through the shared-memory staging row (0..8)
-#ifdef SKV_TC_PROFILE
-  long long* prof;          // [ctas][8] phase cycle counters (diagnostic builds only)
-#endif
 };
 
 template <int GROUPS>
@@ -118,27 +115,13 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
     const bool relu = P.act == SKV_ACT_RELU_SQ;
 
-#ifdef SKV_TC_PROFILE
-    long long pw = 0, pb = 0, pf = 0;
-    const long long pstart = clock64();
-#define SKV_T(x) const long long x = clock64()
-#define SKV_ACC(a, expr) a += (expr)
-#else
-#define SKV_T(x)
-#define SKV_ACC(a, expr)
-#endif
     auto chunk_body = [&](int ci, int s, uint32_t(&sv)[kChunkKeys]) {
-      SKV_T(c0);
       const uint4 zc = znext;
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
       const uint32_t row = smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes) + t_off;
       if (ci >= kStages) {
         mbar_wait(empty + s * GROUPS + grp, (uint32_t)((ci / kStages) - 1) & 1u, abort_flag, P.status,
                   kStatusTimeoutFwd);
-        SKV_T(c1);
-#ifdef SKV_TC_PROFILE
-        pw += c1 - c0;
-#endif
         if (valid) {
 #pragma unroll
           for (int q = 0; q < kChunkKeys; ++q) {
@@ -165,14 +148,8 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
         }
         if (arow) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
       }
-      SKV_T(c2);
       fence_async_smem();
       mbar_arrive(full + s * GROUPS + grp);
-#ifdef SKV_TC_PROFILE
-      const long long c3 = clock64();
-      pf += c3 - c2;
-      pb += c2 - c0;
-#endif
     };
 
     for (int ci = 0; ci < nch; ci += kStages) {
@@ -180,12 +157,6 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
       if (ci + 1 < nch) chunk_body(ci + 1, 1, saved[1]);
     }
 
-#ifdef SKV_TC_PROFILE
-    if (tid == 0) {
-      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-      o[0] = clock64() - pstart; o[1] = pw; o[2] = pb; o[3] = pf;
-    }
-#endif
     // epilogue: accumulator -> float32 partial of this key split
     mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutFwd);
     tc_fence_after();
@@ -208,25 +179,14 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
       const int ksteps = kChunkKeys * L / 16;
       const uint32_t a_hi = desc_hi(P.a_sbo), b_hi = desc_hi(P.b_sbo);
       const uint32_t a_step = (2u * 2048u) >> 4, b_step = (2u * (uint32_t)(r / 8) * 128u) >> 4;   // per K=16 step
-#ifdef SKV_TC_PROFILE
-      long long mc = 0, mf = 0, mi = 0;
-      const long long mstart = clock64();
-#endif
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % kStages;
         const uint32_t par = (uint32_t)(ci / kStages) & 1u;
         const int cs = ci % CS;
-        SKV_T(m0);
         mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
-        SKV_T(m1);
-#ifdef SKV_TC_PROFILE
-        mc += m1 - m0;
-#endif
         const uint32_t b_lo0 = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
         for (int grp = 0; grp < GROUPS; ++grp) {
-          SKV_T(m2);
           mbar_wait(full + s * GROUPS + grp, par, abort_flag, P.status, kStatusTimeoutFwd);
-          SKV_T(m3);
           tc_fence_after();
           uint32_t a_lo = desc_lo(smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes), P.a_lbo);
           uint32_t b_lo = b_lo0;
@@ -238,19 +198,10 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
             umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, 1u);
           }
           umma_commit(empty + s * GROUPS + grp);
-#ifdef SKV_TC_PROFILE
-          const long long m4 = clock64();
-          mf += m3 - m2;
-          mi += m4 - m3;
-#endif
         }
         umma_commit(cempty + cs);
       }
       umma_commit(done);
-#ifdef SKV_TC_PROFILE
-      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-      o[4] = clock64() - mstart; o[5] = mc; o[6] = mf; o[7] = mi;
-#endif
     }
   } else {
     // ------------------------------------------------------------------ code-table loader
@@ -360,10 +311,6 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
     const uint32_t srow = smem_u32(stage_base) + (uint32_t)(tid * SW * 4);
     const int nstaged = P.nstaged;
-#ifdef SKV_TC_PROFILE
-    long long pw = 0, pb = 0, pf = 0;
-    const long long pstart = clock64();
-#endif
     for (int ci = 0; ci < nch; ++ci) {
       const uint4 zc = znext;
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
@@ -373,12 +320,10 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       // half run while the other half is being built, so the producers do not wait for them.
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        SKV_T(c0);
         if (ci > 0) {
           mbar_wait(empty + grp * 2 + half, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
           tc_fence_after();
         }
-        SKV_T(c1);
 #pragma unroll
         for (int qq = 0; qq < kHalfKeys; ++qq) {
           const int q = half * kHalfKeys + qq;
@@ -420,23 +365,12 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
           else aw[q >> 1] = __float_as_uint(a);
         }
-        SKV_T(c2);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(full + grp * 2 + half);
-#ifdef SKV_TC_PROFILE
-        const long long c3 = clock64();
-        pw += c1 - c0; pb += c2 - c1; pf += c3 - c2;
-#endif
       }
       if (arow && valid) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
     }
-#ifdef SKV_TC_PROFILE
-    if (tid == 0) {
-      long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-      o[0] = clock64() - pstart; o[1] = pw; o[2] = pb; o[3] = pf;
-    }
-#endif
     // epilogue: accumulator -> float32 partial of this key split
     mbar_wait(done + grp, 0, abort_flag, P.status, kStatusTimeoutFwd);
     tc_fence_after();
@@ -462,23 +396,14 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       const uint32_t b_step = (2u * (uint32_t)(r / 8) * 128u) >> 4;          // per K=16 step
       const uint32_t a_addr0 = tmem_base + (uint32_t)grp * grp_cols;
       const uint32_t d_addr = a_addr0 + (uint32_t)(kChunkKeys * HLP);
-#ifdef SKV_TC_PROFILE
-      long long mc = 0, mf = 0, mi = 0;
-      const long long mstart = clock64();
-#endif
       for (int ci = 0; ci < nch; ++ci) {
         const int cs = ci % CS;
-        SKV_T(m0);
         mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
-        SKV_T(m1);
-        SKV_ACC(mc, m1 - m0);
         uint32_t b_lo = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
         uint32_t a_addr = a_addr0;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          SKV_T(m2);
           mbar_wait(full + grp * 2 + half, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutFwd);
-          SKV_T(m3);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < kHalfSteps; ++ks) {     // 8 columns of A (16 K elements) per step
@@ -487,19 +412,10 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
             b_lo += b_step;
           }
           umma_commit(empty + grp * 2 + half);
-          SKV_T(m4);
-          SKV_ACC(mf, m3 - m2);
-          SKV_ACC(mi, m4 - m3);
         }
         umma_commit(cempty + cs);
       }
       umma_commit(done + grp);
-#ifdef SKV_TC_PROFILE
-      if (grp == 0) {
-        long long* o = P.prof + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-        o[4] = clock64() - mstart; o[5] = mc; o[6] = mf; o[7] = mi;
-      }
-#endif
     }
   } else {
     // ------------------------------------------------------------------ code-table loader
@@ -562,11 +478,6 @@ __global__ void tc_finalize_kernel(const float* __restrict__ partial, int splits
   }
 }
 
-#ifdef SKV_TC_PROFILE
-}  // namespace
-long long* g_prof = nullptr;   // set by the diagnostic harness before calling forward()
-namespace {
-#endif
 
 struct FwdPlan {
   int groups, splits, chunks_per_split, cstages;
@@ -696,9 +607,6 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.status = c.status;
   P.cstages = f.cstages;
   P.nstaged = 4;            // measured best at the d20 shape (3..5 within 1 %)
-#ifdef SKV_TC_PROFILE
-  P.prof = g_prof;
-#endif
   // A: Phi tile, K-major; core matrices of 8 tokens x 8 k: 128 B apart along tokens, 2048 B along k
   P.a_lbo = 2048;
   P.a_sbo = 128;
