@@ -199,6 +199,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="token chunks the end-to-end step is pipelined over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg = make_cfg(args.gpus)
@@ -325,7 +326,7 @@ def main():
         # chunk i+1, the operator's forward+backward on chunk i and the device-to-host copies of chunk
         # i-1 overlap (PCIe is full duplex); dC is accumulated across the chunks on the device, as
         # autograd does for micro-batches, and copied back once.
-        NCH = 8 if N % 8 == 0 and N >= 8192 else 1
+        NCH = args.e2e_chunks if N % args.e2e_chunks == 0 and N >= 1024 * args.e2e_chunks else 1
         rows = N // NCH
         s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         state = dict(prev_comp=[None] * NCH)

@@ -31,16 +31,31 @@ struct Knot {
   float tau;
   bool in_range;
   bool clamp_active;
+  uint32_t tbits;   // bit pattern of 2^23 + bin as float32: kKnotBias + bin
 };
 
+// Bit pattern of 2^23 as float32; Knot::tbits - kKnotBias is the interval index.
+constexpr uint32_t kKnotBias = 0x4B000000u;
+
+// The arithmetic is arranged for the instruction mix of the kernels that call it for every
+// (token, key) pair, without changing any result:
+//  * u is formed as fma(z - lo, scale, +0): the same rounding as the plain product, and a product
+//    of -0 becomes +0, so that the two range tests are single unsigned comparisons of the bit
+//    pattern (non-negative floats order like their bit patterns; negative values and NaN have
+//    patterns above that of any grid bound);
+//  * floor(u_c) is taken by adding 2^23 rounding down (u_c lies in [0, G-1], far below 2^22, so the
+//    sum is exactly 2^23 + floor(u_c)) instead of a float -> int -> float round trip.
 __device__ __forceinline__ Knot knot_of(float z, const GridParams& g) {
   Knot k;
-  float u = __fmul_rn(__fsub_rn(z, g.lo), g.scale);
-  k.in_range = (u >= 0.0f) && (u <= g.Gf);
-  k.clamp_active = (u >= 0.0f) && (u <= g.Gm1f);
-  float uc = fminf(fmaxf(u, 0.0f), g.Gm1f);   // NaN clamps to 0
-  k.bin = __float2int_rz(uc);                  // uc >= 0: truncation is floor
-  k.tau = __fsub_rn(uc, (float)k.bin);         // exact, in [0, 1)
+  const float u = __fmaf_rn(__fsub_rn(z, g.lo), g.scale, 0.0f);
+  const uint32_t ub = __float_as_uint(u);
+  k.in_range = ub <= __float_as_uint(g.Gf);
+  k.clamp_active = ub <= __float_as_uint(g.Gm1f);
+  const float uc = fminf(fmaxf(u, 0.0f), g.Gm1f);   // NaN clamps to 0
+  const float t = __fadd_rd(uc, 8388608.0f);
+  k.tbits = __float_as_uint(t);
+  k.bin = (int)(k.tbits & 0x007fffffu);
+  k.tau = __fsub_rn(uc, __fsub_rn(t, 8388608.0f));  // exact, in [0, 1)
   return k;
 }
 

@@ -273,8 +273,9 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
           else tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufb);
         }
         const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
-        const float u = __fmul_rn(__fsub_rn(zz, P.g.lo), P.g.scale);
-        const bool active = (u >= 0.0f) && (u <= P.g.Gm1f);
+        // same u and the same single-comparison range test as knot_of
+        const float u = __fmaf_rn(__fsub_rn(zz, P.g.lo), P.g.scale, 0.0f);
+        const bool active = __float_as_uint(u) <= __float_as_uint(P.g.Gm1f);
         const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
         const float acc = (q & 1) ? dz_key_sum<LB>(bufb, uc) : dz_key_sum<LB>(bufa, uc);
         float o = active ? coef * acc : 0.0f;

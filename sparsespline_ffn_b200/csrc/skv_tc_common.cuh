@@ -179,6 +179,14 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// ReLU(z)^2 of two packed bf16 values.  The product of two bf16 values is exact in float32, so the
+// packed multiply (one rounding to bf16) equals float32 arithmetic followed by a cast.
+__device__ __forceinline__ uint32_t relu_sq_bf2(uint32_t w) {
+  __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w);
+  v = __hmax2(v, __float2bfloat162_rn(0.0f));
+  v = __hmul2(v, v);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
@@ -197,13 +205,12 @@ __device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t
                                          uint32_t& wo0, uint32_t& wo1) {
   const Knot k = knot_of(zz, g);
   const float t = k.tau, omt = 1.0f - t;
-  const float m = k.in_range ? 1.0f : 0.0f;
-  const float hm = 0.5f * m;
+  const float hm = k.in_range ? 0.5f : 0.0f;
   const float B0 = (hm * omt) * omt;
   const float B2 = (hm * t) * t;
-  const float B1 = (m - B0) - B2;
+  const float B1 = fmaf(2.0f, hm, -B0) - B2;          // (m - B0) - B2 with m = 2 * hm, same roundings
   const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
-  const uint32_t sh = ((uint32_t)k.bin & 1u) << 4;
+  const uint32_t sh = (k.tbits & 1u) << 4;
   x0 = p01 << sh;
   x1 = __funnelshift_l(p01, p2, sh);
   const uint32_t s0 = wq + ((uint32_t)k.bin >> 1), s1 = s0 + 1u;
@@ -212,21 +219,22 @@ __device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t
 }
 
 // Knot-dependent part of phi_pair only: the two f16x2 words and the index (bin >> 1) of the first
-// one within the key's L/2 words.
+// one within the key's L/2 words, returned with the bias kWordBias (the callers fold the bias into
+// the constants they compare or add it to, which saves an instruction per pair).
+constexpr uint32_t kWordBias = kKnotBias >> 1;
 __device__ __forceinline__ void phi_pair_words(float zz, const GridParams& g, uint32_t& x0, uint32_t& x1,
                                                uint32_t& wp) {
   const Knot k = knot_of(zz, g);
   const float t = k.tau, omt = 1.0f - t;
-  const float m = k.in_range ? 1.0f : 0.0f;
-  const float hm = 0.5f * m;
+  const float hm = k.in_range ? 0.5f : 0.0f;
   const float B0 = (hm * omt) * omt;
   const float B2 = (hm * t) * t;
-  const float B1 = (m - B0) - B2;
+  const float B1 = fmaf(2.0f, hm, -B0) - B2;          // (m - B0) - B2 with m = 2 * hm, same roundings
   const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
-  const uint32_t sh = ((uint32_t)k.bin & 1u) << 4;
+  const uint32_t sh = (k.tbits & 1u) << 4;
   x0 = p01 << sh;
   x1 = __funnelshift_l(p01, p2, sh);
-  wp = (uint32_t)k.bin >> 1;
+  wp = k.tbits >> 1;
 }
 
 // Store N consecutive 32-bit columns of this thread's tensor-memory lane (lane = 32 * (warp % 4) + lane id).

@@ -49,7 +49,6 @@ struct FwdParams {
   int32_t* status;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   int cstages;              // depth of the code-table ring (2..4)
-  int nstaged;              // keys per chunk placed through the shared-memory staging row (0..8)
 };
 
 template <int GROUPS>
@@ -246,7 +245,20 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 // accumulator; with four groups (512 tokens per CTA, 16 producer warps) the other groups keep the
 // SM busy while one group waits for its MMAs.
 // ---------------------------------------------------------------------------------------------
-template <int GROUPS, int HL, bool RELU>
+// Keys of each half chunk (of four) that are placed through the staging row; the others use
+// compare/select chains.  Two of four balances the load/store data pipe against the ALU pipe
+// (measured at the d20 shape: 1 -> 1.07 ms, 2 -> 0.99 ms, 3 -> 1.17 ms, 4 -> 1.42 ms; reading the
+// rows back with 8- or 4-byte loads from rows with fewer store bank conflicts changes nothing).
+constexpr int kStagedPerHalf = 2;
+
+// Words per staging row of a producer thread for rows of hlp words: a multiple of four words with
+// an odd number of 16-byte units, so that the 16-byte loads of eight consecutive threads start in
+// eight different bank quads.
+__host__ __device__ constexpr int stage_row_words(int hlp) {
+  return (hlp % 8 == 4) ? hlp : (hlp + 7) / 8 * 8 + 4;
+}
+
+template <int GROUPS, int HL, bool RELU, int NSTH>
 __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(const FwdParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // Keys are padded to HLP words (an even count), so that half a chunk (4 keys) is a whole number
@@ -260,11 +272,11 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   uint8_t* c_base = smem;                                          // [cstage][c_bytes]
   // One private staging row of SW words per producer thread.  Placing the two non-zero words of a
   // row segment costs about thirty compare/select instructions on the half-rate ALU pipe; for
-  // the first P.nstaged keys of every chunk the thread instead stores the two words into its
+  // NSTH of the four keys of every half chunk the thread instead stores the two words into its
   // (zeroed) staging row at the dynamic position, reads the row back with three 16-byte loads and
   // zeroes the two words again, which moves that work to the load/store pipe.  SW/4 is odd, so
   // the rows of eight consecutive threads start in eight different bank quads.
-  constexpr int SW = (HLP % 8 == 4) ? HLP : (HLP + 7) / 8 * 8 + 4;
+  constexpr int SW = stage_row_words(HLP);
   uint8_t* stage_base = c_base + (size_t)CS * c_bytes;             // [128*GROUPS][SW words]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_base + (size_t)128 * GROUPS * SW * 4);
   uint64_t* full = bars;                          // [group][half]  producers -> MMA
@@ -310,12 +322,16 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
     const uint32_t srow = smem_u32(stage_base) + (uint32_t)(tid * SW * 4);
-    const int nstaged = P.nstaged;
+    const uint32_t srow_biased = srow - (kWordBias << 2);          // wp carries the bias kWordBias
     for (int ci = 0; ci < nch; ++ci) {
       const uint4 zc = znext;
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
       const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
+      // phi(z) of the chunk's eight keys in packed bf16 arithmetic: the product of two bf16 values is
+      // exact in float32, so one rounding to bf16 gives the same result as float32 arithmetic and a cast
       uint32_t aw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) aw[i] = RELU ? relu_sq_bf2(zw[i]) : zw[i];
       // The group's A columns are written and consumed in two halves of 4 keys: the MMAs of one
       // half run while the other half is being built, so the producers do not wait for them.
 #pragma unroll
@@ -324,47 +340,64 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           mbar_wait(empty + grp * 2 + half, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
           tc_fence_after();
         }
+        // The first NSTH keys of the half go through the staging row: their stores and loads are
+        // issued first, the select chains of the other keys run while those loads are in flight,
+        // and the staged rows are written to tensor memory last.
+        uint32_t Ws[NSTH > 0 ? NSTH : 1][HLP];
 #pragma unroll
-        for (int qq = 0; qq < kHalfKeys; ++qq) {
+        for (int qq = 0; qq < NSTH; ++qq) {
           const int q = half * kHalfKeys + qq;
           const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
           uint32_t x0, x1, wp;
           phi_pair_words(zz, P.g, x0, x1, wp);   // rows past N read z = 0; their accumulator rows are never stored
-          uint32_t W[HLP];
-          if (q < nstaged) {
-            const uint32_t pos = srow + wp * 4u;
-            sts32(pos, x0);
-            sts32(pos + 4u, x1);
+          const uint32_t pos = srow_biased + wp * 4u;
+          sts32(pos, x0);
+          sts32(pos + 4u, x1);
 #pragma unroll
-            for (int i = 0; i < HLP; i += 4) {
-              if (i + 4 <= HLP) {
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(W[i]), "=r"(W[i + 1]), "=r"(W[i + 2]), "=r"(W[i + 3])
-                             : "r"(srow + (uint32_t)i * 4u)
-                             : "memory");
-              } else {
-                asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];"
-                             : "=r"(W[i]), "=r"(W[i + 1])
-                             : "r"(srow + (uint32_t)i * 4u)
-                             : "memory");
-              }
+          for (int i = 0; i < HLP; i += 4) {
+            if (i + 4 <= HLP) {
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(Ws[qq][i]), "=r"(Ws[qq][i + 1]), "=r"(Ws[qq][i + 2]), "=r"(Ws[qq][i + 3])
+                           : "r"(srow + (uint32_t)i * 4u)
+                           : "memory");
+            } else {
+              asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];"
+                           : "=r"(Ws[qq][i]), "=r"(Ws[qq][i + 1])
+                           : "r"(srow + (uint32_t)i * 4u)
+                           : "memory");
             }
-            sts32(pos, 0u);
-            sts32(pos + 4u, 0u);
-          } else {
-            W[0] = wp == 0u ? x0 : 0u;
+          }
+          sts32(pos, 0u);
+          sts32(pos + 4u, 0u);
+        }
 #pragma unroll
-            for (int i = 1; i < HL - 1; ++i) W[i] = wp == (uint32_t)i ? x0 : (wp == (uint32_t)(i - 1) ? x1 : 0u);
-            W[HL - 1] = wp == (uint32_t)(HL - 2) ? x1 : 0u;
+        for (int qq = NSTH; qq < kHalfKeys; ++qq) {
+          const int q = half * kHalfKeys + qq;
+          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+          uint32_t x0, x1, wp;
+          phi_pair_words(zz, P.g, x0, x1, wp);
+          // Placement at word-pair granularity: wp = 2 * qd + s.  The two words land in pair qd as
+          // (x0, x1) when s = 0, or as (0, x0) there and (x1, 0) in pair qd + 1 when s = 1.
+          uint32_t W[HLP];
+          const bool odd = (wp & 1u) != 0u;
+          const uint32_t qd = wp >> 1;
+          const uint32_t y0 = odd ? 0u : x0, y1 = odd ? x0 : x1, y2 = odd ? x1 : 0u;
+          constexpr uint32_t kPairBias = kWordBias >> 1;
+          constexpr int kLastPair = (HL - 2) >> 1;               // largest qd: bin <= L - 3
+          bool hit[HLP / 2 + 1];
 #pragma unroll
-            for (int i = HL; i < HLP; ++i) W[i] = 0u;
+          for (int i = 0; i < HLP / 2; ++i) hit[i] = i <= kLastPair && qd == kPairBias + (uint32_t)i;
+#pragma unroll
+          for (int i = 0; i < HLP / 2; ++i) {
+            const uint32_t carry = (i > 0 && hit[i - 1]) ? y2 : 0u;
+            W[2 * i] = hit[i] ? y0 : carry;
+            W[2 * i + 1] = hit[i] ? y1 : 0u;
           }
           tmem_st_words<HLP>(lane_addr + (uint32_t)(q * HLP), W);
-          const float zp = fmaxf(zz, 0.0f);
-          const float a = RELU ? zp * zp : zz;
-          if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
-          else aw[q >> 1] = __float_as_uint(a);
         }
+#pragma unroll
+        for (int qq = 0; qq < NSTH; ++qq)
+          tmem_st_words<HLP>(lane_addr + (uint32_t)((half * kHalfKeys + qq) * HLP), Ws[qq]);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(full + grp * 2 + half);
@@ -500,7 +533,7 @@ bool plan_forward(const skv_problem& p, FwdPlan* out) {
     int groups = 512 / (kChunkKeys * hlp + p.r);
     if (groups > 4) groups = 4;
     const size_t c_bytes = (size_t)kChunkKeys * 2 * hlp * p.r * 2;
-    const int sw = (hlp % 8 == 4) ? hlp : (hlp + 7) / 8 * 8 + 4;      // staging-row words per producer thread
+    const int sw = stage_row_words(hlp);               // staging-row words per producer thread
     const size_t stage_bytes = (size_t)128 * groups * sw * 4;
     int cstages = (int)((kSmemLimit - 512 - stage_bytes) / c_bytes);
     if (cstages > kMaxTaCStages) cstages = kMaxTaCStages;
@@ -606,7 +639,6 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.chunks_per_split = f.chunks_per_split;
   P.status = c.status;
   P.cstages = f.cstages;
-  P.nstaged = 4;            // measured best at the d20 shape (3..5 within 1 %)
   // A: Phi tile, K-major; core matrices of 8 tokens x 8 k: 128 B apart along tokens, 2048 B along k
   P.a_lbo = 2048;
   P.a_sbo = 128;
@@ -620,21 +652,21 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   if (f.ta) {
     const unsigned threads = 160 * f.groups + 32;
     const int hl = p.L / 2;
+#define SKV_TA_LAUNCH(G_, HL_, RELU_)                                                                                \
+  {                                                                                                                  \
+    err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, RELU_, kStagedPerHalf>,                     \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem);                            \
+    if (err == cudaSuccess)                                                                                          \
+      tc_forward_ta_kernel<G_, HL_, RELU_, kStagedPerHalf><<<grid, threads, f.smem, c.stream>>>(P);      \
+  }
 #define SKV_TA_CASE(G_, HL_)                                                                                         \
   if (f.groups == G_ && hl == HL_) {                                                                                 \
-    if (p.activation == SKV_ACT_RELU_SQ) {                                                                           \
-      err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                 (int)f.smem);                                                                       \
-      if (err == cudaSuccess) tc_forward_ta_kernel<G_, HL_, true><<<grid, threads, f.smem, c.stream>>>(P);           \
-    } else {                                                                                                         \
-      err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                 (int)f.smem);                                                                       \
-      if (err == cudaSuccess) tc_forward_ta_kernel<G_, HL_, false><<<grid, threads, f.smem, c.stream>>>(P);          \
-    }                                                                                                                \
+    if (p.activation == SKV_ACT_RELU_SQ) SKV_TA_LAUNCH(G_, HL_, true) else SKV_TA_LAUNCH(G_, HL_, false)             \
   }
     SKV_TA_CASE(1, 8) SKV_TA_CASE(2, 8) SKV_TA_CASE(3, 8) SKV_TA_CASE(4, 8)
     SKV_TA_CASE(1, 11) SKV_TA_CASE(2, 11) SKV_TA_CASE(3, 11) SKV_TA_CASE(4, 11)
     SKV_TA_CASE(1, 21) SKV_TA_CASE(2, 21)
+#undef SKV_TA_LAUNCH
 #undef SKV_TA_CASE
   } else if (f.groups == 2) {
     err = cudaFuncSetAttribute(tc_forward_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem);
