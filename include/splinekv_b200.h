@@ -39,7 +39,7 @@ enum skv_error {
 };
 
 enum skv_dtype { SKV_BF16 = 0, SKV_F32 = 1 };
-enum skv_activation { SKV_ACT_RELU_SQ = 0, SKV_ACT_IDENTITY = 1 };
+enum skv_activation { SKV_ACT_RELU_SQ = 0, SKV_ACT_IDENTITY = 1, SKV_ACT_GELU = 2 };
 /* SKV_IMPL_AUTO picks the tcgen05 kernels when the shape is eligible (bf16, r a multiple of 16
  * up to 128, even L, h a multiple of 8, 16-byte aligned rows) and the CUDA-core kernels otherwise. */
 enum skv_impl { SKV_IMPL_AUTO = 0, SKV_IMPL_SIMT = 1, SKV_IMPL_TCGEN05 = 2 };

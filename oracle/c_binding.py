@@ -62,7 +62,7 @@ def _scale(grid_lo, grid_hi, G) -> float:
     return float(np.float32(float(G) / (float(grid_hi) - float(grid_lo))))
 
 
-_ACT = {"relu_sq": 0, "identity": 1}
+_ACT = {"relu_sq": 0, "identity": 1, "gelu": 2}
 
 
 def num_threads() -> int:

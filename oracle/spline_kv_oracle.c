@@ -21,6 +21,7 @@
  *
  * Build: gcc -O2 -fopenmp -ffp-contract=off -shared -fPIC spline_kv_oracle.c -o libskv_oracle.so
  */
+#include <math.h>
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -81,7 +82,26 @@ void skvo_knot_index(const float *z, int64_t zs, int64_t N, int h,
             bins[n * h + j] = skvo_eval(z[n * zs + j], lo, scale, G).bin;
 }
 
-/* act: 0 = relu_sq, 1 = identity.
+/* phi and phi' of the base path (rl_spline_kv_reference.py:78-85; the gelu of F.gelu is the exact
+ * erf form, its derivative Phi(z) + z * pdf(z) is what autograd returns at
+ * flash_spline_feature_autograd.py:229-235). */
+static double skvo_act(float zz, int act)
+{
+    if (act == 0) return zz > 0.0f ? (double)zz * (double)zz : 0.0;
+    if (act == 2) return 0.5 * (double)zz * (1.0 + erf((double)zz * 0.70710678118654752440));
+    return (double)zz;
+}
+static double skvo_act_grad(float zz, int act)
+{
+    if (act == 0) return zz > 0.0f ? 2.0 * (double)zz : 0.0;
+    if (act == 2) {
+        double x = (double)zz;
+        return 0.5 * (1.0 + erf(x * 0.70710678118654752440)) + x * exp(-0.5 * x * x) * 0.39894228040143267794;
+    }
+    return 1.0;
+}
+
+/* act: 0 = relu_sq, 1 = identity, 2 = gelu.
  * a[N*h] (may be NULL) receives phi(z); delta[N*r] receives lambda * delta. */
 void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, int L, int r,
                   float lo, float scale, float lambda, int act, float *a, float *delta)
@@ -95,7 +115,7 @@ void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, 
             for (int c = 0; c < r; ++c) acc[c] = 0.0;
             for (int j = 0; j < h; ++j) {
                 float zz = z[n * zs + j];
-                if (a) a[n * h + j] = act == 0 ? (zz > 0.0f ? zz * zz : 0.0f) : zz;
+                if (a) a[n * h + j] = (float)skvo_act(zz, act);
                 skvo_basis e = skvo_eval(zz, lo, scale, G);
                 const float *row = C + ((size_t)j * L + e.bin) * r;
                 double b0 = e.B[0], b1 = e.B[1], b2 = e.B[2];
@@ -136,7 +156,7 @@ void skvo_backward(const float *z, int64_t zs, const float *C,
             }
             double v = (double)lambda * (double)scale * (e.dB[0] * s0 + e.dB[1] * s1 + e.dB[2] * s2);
             if (g_a) {
-                double dphi = act == 0 ? (zz > 0.0f ? 2.0 * (double)zz : 0.0) : 1.0;
+                double dphi = skvo_act_grad(zz, act);
                 v += (double)g_a[n * gas + j] * dphi;
             }
             dz[n * h + j] = (float)v;

@@ -34,9 +34,13 @@ oracle is closer to the exact value than any float32 summation order.
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 
-ACTIVATIONS = ("relu_sq", "identity")
+_erf = np.vectorize(math.erf, otypes=[np.float64])
+
+ACTIVATIONS = ("relu_sq", "identity", "gelu")
 
 
 def grid_scale(grid_lo: float, grid_hi: float, G: int) -> np.float32:
@@ -85,6 +89,9 @@ def activation(z32: np.ndarray, name: str) -> np.ndarray:
         return np.where(z32 > 0, z32 * z32, np.float32(0.0)).astype(np.float32)
     if name == "identity":
         return np.asarray(z32, dtype=np.float32)
+    if name == "gelu":          # F.gelu: the exact erf form
+        z = np.asarray(z32, dtype=np.float64)
+        return (0.5 * z * (1.0 + _erf(z * 0.7071067811865476))).astype(np.float32)
     raise ValueError(name)
 
 
@@ -93,6 +100,10 @@ def activation_grad(z32: np.ndarray, name: str) -> np.ndarray:
         return np.where(z32 > 0, np.float32(2.0) * z32, np.float32(0.0)).astype(np.float32)
     if name == "identity":
         return np.ones_like(z32, dtype=np.float32)
+    if name == "gelu":          # Phi(z) + z * pdf(z), what autograd returns for F.gelu
+        z = np.asarray(z32, dtype=np.float64)
+        return (0.5 * (1.0 + _erf(z * 0.7071067811865476))
+                + z * np.exp(-0.5 * z * z) * 0.3989422804014327).astype(np.float32)
     raise ValueError(name)
 
 

@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libsplinekv_b200.so")
 
 SKV_BF16, SKV_F32 = 0, 1
-SKV_ACT = {"relu_sq": 0, "identity": 1}
+SKV_ACT = {"relu_sq": 0, "identity": 1, "gelu": 2}
 SKV_IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
 SKV_OP_FORWARD, SKV_OP_BACKWARD = 0, 1
 

@@ -19,7 +19,8 @@ int validate(const skv_problem* p) {
   if (p->N < 0 || p->h < 1 || p->L < 4 || p->r < 1) return SKV_ERR_SHAPE;
   if (p->N > (int64_t)1 << 40 || p->h > (1 << 24) || p->L > 4096) return SKV_ERR_SHAPE;
   if (p->dtype != SKV_BF16 && p->dtype != SKV_F32) return SKV_ERR_UNSUPPORTED;
-  if (p->activation != SKV_ACT_RELU_SQ && p->activation != SKV_ACT_IDENTITY) return SKV_ERR_UNSUPPORTED;
+  if (p->activation != SKV_ACT_RELU_SQ && p->activation != SKV_ACT_IDENTITY && p->activation != SKV_ACT_GELU)
+    return SKV_ERR_UNSUPPORTED;
   if (p->impl != SKV_IMPL_AUTO && p->impl != SKV_IMPL_SIMT && p->impl != SKV_IMPL_TCGEN05)
     return SKV_ERR_UNSUPPORTED;
   if (p->r > 256) return SKV_ERR_UNSUPPORTED;

@@ -79,11 +79,17 @@ __device__ __forceinline__ void basis_derivs(const Knot& k, float& d0, float& d1
 
 // phi and phi' of the base path (rl_spline_kv_reference.py:78-85,
 // flash_spline_feature_autograd.py:227-237).
+// gelu is the exact erf form of torch.nn.functional.gelu; its derivative Phi(z) + z * pdf(z) is what
+// autograd returns for it.
+__device__ __forceinline__ float gelu_fwd(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad(float z) {
+  return 0.5f * (1.0f + erff(z * 0.70710678118654752f)) + z * expf(-0.5f * z * z) * 0.39894228040143268f;
+}
 __device__ __forceinline__ float act_fwd(float z, int act) {
-  return act == SKV_ACT_RELU_SQ ? (z > 0.0f ? z * z : 0.0f) : z;
+  return act == SKV_ACT_RELU_SQ ? (z > 0.0f ? z * z : 0.0f) : act == SKV_ACT_GELU ? gelu_fwd(z) : z;
 }
 __device__ __forceinline__ float act_grad(float z, int act) {
-  return act == SKV_ACT_RELU_SQ ? (z > 0.0f ? 2.0f * z : 0.0f) : 1.0f;
+  return act == SKV_ACT_RELU_SQ ? (z > 0.0f ? 2.0f * z : 0.0f) : act == SKV_ACT_GELU ? gelu_grad(z) : 1.0f;
 }
 
 template <typename T> __device__ __forceinline__ float ld_f32(const T* p);

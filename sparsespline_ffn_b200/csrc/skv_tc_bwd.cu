@@ -165,19 +165,26 @@ __device__ __forceinline__ void tmem_wait_key(uint32_t (&r)[LB][8]) {
                  : "memory");
 }
 
-// S_0 + sum_m sat(uc - m) * S_{m+1} over the 8*LB columns of one key (padding columns are zero in
-// the table image and their weight sat(uc - m) is zero as well, since uc <= G-1 < m).
+// S_0 + sum_m sat(uc - m) * S_{m+1} over the first NC of the 8*LB columns of one key.  Columns
+// L-1 and up are padding (zero rows of the table image, and their weight sat(uc - m) is zero as
+// well since uc <= G-1 < m); with NC = L-1 known at compile time they cost nothing.
 // Columns are taken in aligned pairs with the packed two-wide float32 FMA of sm_100
 // (fma.rn.f32x2): weight 1 for column 0, sat(uc - (m-1)) for column m.
-template <int LB>
+template <int LB, int NC>
 __device__ __forceinline__ float dz_key_sum(const uint32_t (&r)[LB][8], float uc) {
   unsigned long long acc2 = 0ull;                     // (0.0f, 0.0f)
+  float tail = 0.0f;
 #pragma unroll
   for (int blk = 0; blk < LB; ++blk) {
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
       const int m = blk * 8 + i;
+      if (m >= NC) continue;
       const float w0 = m == 0 ? 1.0f : __saturatef(uc - (float)(m - 1));
+      if (m + 1 >= NC) {                              // last column of an odd count
+        tail = w0 * __uint_as_float(r[blk][i]);
+        continue;
+      }
       const float w1 = __saturatef(uc - (float)m);
       unsigned long long w2, s2;
       asm("mov.b64 %0, {%1, %2};" : "=l"(w2) : "f"(w0), "f"(w1));
@@ -187,12 +194,14 @@ __device__ __forceinline__ float dz_key_sum(const uint32_t (&r)[LB][8], float uc
   }
   float a0, a1;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc2));
-  return a0 + a1;
+  return (a0 + a1) + tail;
 }
 
 constexpr int kTStages = 4;
 
-template <int GROUPS, int LB>
+// RELU: the base path is ReLU^2 (compile-time, so that the code of the other activations stays
+// out of the hot loop); otherwise P.act (identity or gelu) is evaluated at run time.
+template <int GROUPS, int LB, int NC, bool RELU>
 __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int r = P.r;
@@ -246,7 +255,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
     float gscale, ginv;
     g_scales(*P.amax_bits, gscale, ginv);
     const float coef = P.coef * ginv;
-    const bool relu = P.act == SKV_ACT_RELU_SQ;
+    const int act = P.act;
     const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * ncols;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
     uint4 ganext = valid && nch > 0 && garow ? __ldg(reinterpret_cast<const uint4*>(garow)) : make_uint4(0, 0, 0, 0);
@@ -277,11 +286,11 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
         const float u = __fmaf_rn(__fsub_rn(zz, P.g.lo), P.g.scale, 0.0f);
         const bool active = __float_as_uint(u) <= __float_as_uint(P.g.Gm1f);
         const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
-        const float acc = (q & 1) ? dz_key_sum<LB>(bufb, uc) : dz_key_sum<LB>(bufa, uc);
+        const float acc = (q & 1) ? dz_key_sum<LB, NC>(bufb, uc) : dz_key_sum<LB, NC>(bufa, uc);
         float o = active ? coef * acc : 0.0f;
         if (garow) {
           const float ga = (q & 1) ? bf_hi(gw[q >> 1]) : bf_lo(gw[q >> 1]);
-          const float dphi = relu ? 2.0f * fmaxf(zz, 0.0f) : 1.0f;
+          const float dphi = RELU ? 2.0f * fmaxf(zz, 0.0f) : act_grad(zz, act);
           o = fmaf(ga, dphi, o);
         }
         outv[q] = o;
@@ -738,13 +747,22 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     dim3 grid((unsigned)tiles, (unsigned)zp.splits);
     const unsigned threads = 128 * zp.groups + 64;
     cudaError_t err = cudaErrorInvalidValue;
-#define SKV_DZ_CASE(G_, LB_)                                                                                      \
-  if (zp.groups == G_ && zp.lb == LB_) {                                                                          \
-    err = cudaFuncSetAttribute(tc_dz_kernel<G_, LB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)zp.smem); \
-    if (err == cudaSuccess) tc_dz_kernel<G_, LB_><<<grid, threads, zp.smem, c.stream>>>(P);                       \
+    // NC_ = L - 1 useful columns per key for the knot counts in common use, all 8 * LB_ otherwise
+#define SKV_DZ_CASE(G_, LB_, NC_, COND_)                                                                           \
+  if (err == cudaErrorInvalidValue && zp.groups == G_ && zp.lb == LB_ && (COND_)) {                                \
+    if (p.activation == SKV_ACT_RELU_SQ) {                                                                         \
+      err = cudaFuncSetAttribute(tc_dz_kernel<G_, LB_, NC_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                 (int)zp.smem);                                                                    \
+      if (err == cudaSuccess) tc_dz_kernel<G_, LB_, NC_, true><<<grid, threads, zp.smem, c.stream>>>(P);           \
+    } else {                                                                                                       \
+      err = cudaFuncSetAttribute(tc_dz_kernel<G_, LB_, NC_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 (int)zp.smem);                                                                    \
+      if (err == cudaSuccess) tc_dz_kernel<G_, LB_, NC_, false><<<grid, threads, zp.smem, c.stream>>>(P);          \
+    }                                                                                                              \
   }
-    SKV_DZ_CASE(2, 1) SKV_DZ_CASE(2, 2) SKV_DZ_CASE(2, 3) SKV_DZ_CASE(2, 4)
-    SKV_DZ_CASE(1, 5) SKV_DZ_CASE(1, 6)
+    SKV_DZ_CASE(2, 3, 21, p.L == 22) SKV_DZ_CASE(2, 2, 15, p.L == 16) SKV_DZ_CASE(1, 6, 41, p.L == 42)
+    SKV_DZ_CASE(2, 1, 8, true) SKV_DZ_CASE(2, 2, 16, true) SKV_DZ_CASE(2, 3, 24, true) SKV_DZ_CASE(2, 4, 32, true)
+    SKV_DZ_CASE(1, 5, 40, true) SKV_DZ_CASE(1, 6, 48, true)
 #undef SKV_DZ_CASE
     note_launches(1);
     if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }

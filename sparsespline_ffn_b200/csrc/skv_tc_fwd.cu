@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 #pragma unroll
       for (int q = 0; q < kChunkKeys; ++q) saved[i][q] = 0;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
-    const bool relu = P.act == SKV_ACT_RELU_SQ;
+    const int act = P.act;
 
     auto chunk_body = [&](int ci, int s, uint32_t(&sv)[kChunkKeys]) {
       const uint4 zc = znext;
@@ -140,8 +140,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
           sts32(row + wo0 * 4u, x0);
           sts32(row + wo1 * 4u, x1);
           sv[q] = wo0 | (wo1 << 16);
-          const float zp = fmaxf(zz, 0.0f);
-          const float a = relu ? zp * zp : zz;
+          const float a = act_fwd(zz, act);
           if (q & 1) aw[q >> 1] = pack_bf2(__uint_as_float(aw[q >> 1]), a);
           else aw[q >> 1] = __float_as_uint(a);
         }
@@ -246,19 +245,12 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 // SM busy while one group waits for its MMAs.
 // ---------------------------------------------------------------------------------------------
 // Keys of each half chunk (of four) that are placed through the staging row; the others use
-// compare/select chains.  Two of four balances the load/store data pipe against the ALU pipe
-// (measured at the d20 shape: 1 -> 1.07 ms, 2 -> 0.99 ms, 3 -> 1.17 ms, 4 -> 1.42 ms; reading the
-// rows back with 8- or 4-byte loads from rows with fewer store bank conflicts changes nothing).
+// compare/select chains.  Two of four balances the load/store data pipe (staging traffic, the
+// tensor-memory stores and the strided global accesses: 72 % busy) against the ALU pipe (63 %)
+// at the d20 shape: 1 -> 1.07 ms, 2 -> 0.95 ms, 3 -> 0.99 ms, 4 -> 1.11 ms.
 constexpr int kStagedPerHalf = 2;
 
-// Words per staging row of a producer thread for rows of hlp words: a multiple of four words with
-// an odd number of 16-byte units, so that the 16-byte loads of eight consecutive threads start in
-// eight different bank quads.
-__host__ __device__ constexpr int stage_row_words(int hlp) {
-  return (hlp % 8 == 4) ? hlp : (hlp + 7) / 8 * 8 + 4;
-}
-
-template <int GROUPS, int HL, bool RELU, int NSTH>
+template <int GROUPS, int HL, int ACT, int NSTH>
 __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(const FwdParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
   // Keys are padded to HLP words (an even count), so that half a chunk (4 keys) is a whole number
@@ -270,13 +262,15 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   const uint32_t c_bytes = (uint32_t)(kChunkKeys * 2 * HLP * r * 2);
   const int CS = P.cstages;
   uint8_t* c_base = smem;                                          // [cstage][c_bytes]
-  // One private staging row of SW words per producer thread.  Placing the two non-zero words of a
-  // row segment costs about thirty compare/select instructions on the half-rate ALU pipe; for
+  // One private staging row of HLP words per producer thread.  Placing the two non-zero words of
+  // a row segment costs about thirty compare/select instructions on the half-rate ALU pipe; for
   // NSTH of the four keys of every half chunk the thread instead stores the two words into its
-  // (zeroed) staging row at the dynamic position, reads the row back with three 16-byte loads and
-  // zeroes the two words again, which moves that work to the load/store pipe.  SW/4 is odd, so
-  // the rows of eight consecutive threads start in eight different bank quads.
-  constexpr int SW = stage_row_words(HLP);
+  // (zeroed) staging row at the dynamic position, reads the row back and zeroes the two words
+  // again, which moves that work to the load/store pipe.  The rows of a warp are interleaved by
+  // lane (word w of lane l at (w * 32 + l) * 4 bytes of the warp's region), so the bank of every
+  // access is the lane and neither the scattered stores nor the loads conflict, whatever the knot
+  // intervals of the 32 tokens are.
+  constexpr int SW = HLP;
   uint8_t* stage_base = c_base + (size_t)CS * c_bytes;             // [128*GROUPS][SW words]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_base + (size_t)128 * GROUPS * SW * 4);
   uint64_t* full = bars;                          // [group][half]  producers -> MMA
@@ -321,8 +315,10 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
     __nv_bfloat16* arow = P.act_out ? P.act_out + (valid ? n : 0) * P.as + (int64_t)chunk_begin * kChunkKeys : nullptr;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * grp_cols;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
-    const uint32_t srow = smem_u32(stage_base) + (uint32_t)(tid * SW * 4);
-    const uint32_t srow_biased = srow - (kWordBias << 2);          // wp carries the bias kWordBias
+    // word w of this thread's staging row lives at (warp * HLP + w) * 128 + lane * 4: its bank is the
+    // lane, whatever w is, so neither the scattered stores nor the loads conflict
+    const uint32_t srow = smem_u32(stage_base) + (uint32_t)(warp * HLP * 128 + lane * 4);
+    const uint32_t srow_biased = srow - (kWordBias << 7);          // wp carries the bias kWordBias
     for (int ci = 0; ci < nch; ++ci) {
       const uint4 zc = znext;
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
@@ -331,7 +327,11 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       // exact in float32, so one rounding to bf16 gives the same result as float32 arithmetic and a cast
       uint32_t aw[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) aw[i] = RELU ? relu_sq_bf2(zw[i]) : zw[i];
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (ACT == SKV_ACT_RELU_SQ) aw[i] = relu_sq_bf2(zw[i]);
+        else if constexpr (ACT == SKV_ACT_GELU) aw[i] = pack_bf2(gelu_fwd(bf_lo(zw[i])), gelu_fwd(bf_hi(zw[i])));
+        else aw[i] = zw[i];
+      }
       // The group's A columns are written and consumed in two halves of 4 keys: the MMAs of one
       // half run while the other half is being built, so the producers do not wait for them.
 #pragma unroll
@@ -350,25 +350,14 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
           uint32_t x0, x1, wp;
           phi_pair_words(zz, P.g, x0, x1, wp);   // rows past N read z = 0; their accumulator rows are never stored
-          const uint32_t pos = srow_biased + wp * 4u;
+          const uint32_t pos = srow_biased + (wp << 7);
           sts32(pos, x0);
-          sts32(pos + 4u, x1);
+          sts32(pos + 128u, x1);
 #pragma unroll
-          for (int i = 0; i < HLP; i += 4) {
-            if (i + 4 <= HLP) {
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(Ws[qq][i]), "=r"(Ws[qq][i + 1]), "=r"(Ws[qq][i + 2]), "=r"(Ws[qq][i + 3])
-                           : "r"(srow + (uint32_t)i * 4u)
-                           : "memory");
-            } else {
-              asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];"
-                           : "=r"(Ws[qq][i]), "=r"(Ws[qq][i + 1])
-                           : "r"(srow + (uint32_t)i * 4u)
-                           : "memory");
-            }
-          }
+          for (int i = 0; i < HLP; ++i)
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(Ws[qq][i]) : "r"(srow + (uint32_t)i * 128u) : "memory");
           sts32(pos, 0u);
-          sts32(pos + 4u, 0u);
+          sts32(pos + 128u, 0u);
         }
 #pragma unroll
         for (int qq = NSTH; qq < kHalfKeys; ++qq) {
@@ -533,7 +522,7 @@ bool plan_forward(const skv_problem& p, FwdPlan* out) {
     int groups = 512 / (kChunkKeys * hlp + p.r);
     if (groups > 4) groups = 4;
     const size_t c_bytes = (size_t)kChunkKeys * 2 * hlp * p.r * 2;
-    const int sw = stage_row_words(hlp);               // staging-row words per producer thread
+    const int sw = hlp;                                            // staging-row words per producer thread
     const size_t stage_bytes = (size_t)128 * groups * sw * 4;
     int cstages = (int)((kSmemLimit - 512 - stage_bytes) / c_bytes);
     if (cstages > kMaxTaCStages) cstages = kMaxTaCStages;
@@ -652,16 +641,18 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   if (f.ta) {
     const unsigned threads = 160 * f.groups + 32;
     const int hl = p.L / 2;
-#define SKV_TA_LAUNCH(G_, HL_, RELU_)                                                                                \
+#define SKV_TA_LAUNCH(G_, HL_, ACT_)                                                                                 \
   {                                                                                                                  \
-    err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, RELU_, kStagedPerHalf>,                     \
+    err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, ACT_, kStagedPerHalf>,                     \
                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem);                            \
     if (err == cudaSuccess)                                                                                          \
-      tc_forward_ta_kernel<G_, HL_, RELU_, kStagedPerHalf><<<grid, threads, f.smem, c.stream>>>(P);      \
+      tc_forward_ta_kernel<G_, HL_, ACT_, kStagedPerHalf><<<grid, threads, f.smem, c.stream>>>(P);      \
   }
 #define SKV_TA_CASE(G_, HL_)                                                                                         \
   if (f.groups == G_ && hl == HL_) {                                                                                 \
-    if (p.activation == SKV_ACT_RELU_SQ) SKV_TA_LAUNCH(G_, HL_, true) else SKV_TA_LAUNCH(G_, HL_, false)             \
+    if (p.activation == SKV_ACT_RELU_SQ) SKV_TA_LAUNCH(G_, HL_, SKV_ACT_RELU_SQ)                                     \
+    else if (p.activation == SKV_ACT_GELU) SKV_TA_LAUNCH(G_, HL_, SKV_ACT_GELU)                                      \
+    else SKV_TA_LAUNCH(G_, HL_, SKV_ACT_IDENTITY)                                                                    \
   }
     SKV_TA_CASE(1, 8) SKV_TA_CASE(2, 8) SKV_TA_CASE(3, 8) SKV_TA_CASE(4, 8)
     SKV_TA_CASE(1, 11) SKV_TA_CASE(2, 11) SKV_TA_CASE(3, 11) SKV_TA_CASE(4, 11)

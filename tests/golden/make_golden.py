@@ -61,6 +61,9 @@ def cases():
     z[:, 1] = specials.flip(0)
     z[:, 2] = rn(n, scale=3.0)
     out["edges"] = dict(z=z, C=rn(h, G + 2, 8, scale=0.1), lo=lo, hi=hi, G=G, act="relu_sq", lam=1.0)
+    # gelu base path (drawn last, so that the cases above keep their values)
+    out["gelu"] = dict(z=rn(36, 24, scale=1.5), C=rn(24, 18, 16, scale=0.1), lo=-4.0, hi=4.0,
+                       G=16, act="gelu", lam=0.75)
     return out
 
 
@@ -105,7 +108,7 @@ def main():
                    in_range=in_range.to(torch.uint8), f=f, dz=dz, dC=dC,
                    delta_only=d.detach(), delta_dz=zt2.grad, delta_dC=Ct2.grad,
                    analytic_dC=dC_an, analytic_dz_spline=dzs_an,
-                   meta=torch.tensor([lo, hi, float(G), lam, 0.0 if act == "relu_sq" else 1.0,
+                   meta=torch.tensor([lo, hi, float(G), lam, {"relu_sq": 0.0, "identity": 1.0, "gelu": 2.0}[act],
                                       1.0 if bool(finite) else 0.0], dtype=torch.float64))
         for k, v in rec.items():
             store[f"{name}/{k}"] = v.detach().numpy()

@@ -99,7 +99,7 @@ def test_argument_validation_matches_the_reference():
     with pytest.raises(ValueError, match=r"G\+spline_order"):
         ops.feature_forward(torch.randn(4, 8), torch.randn(8, 21, 16), -3, 3, 20)
     with pytest.raises(ValueError, match="activation"):
-        ops.feature_forward(torch.randn(4, 8), torch.randn(8, 22, 16), -3, 3, 20, activation="gelu")
+        ops.feature_forward(torch.randn(4, 8), torch.randn(8, 22, 16), -3, 3, 20, activation="swish")
     with pytest.raises(ValueError, match="fwd_kernel"):
         FlashSplineFeature.apply(torch.randn(4, 8).requires_grad_(), torch.randn(8, 22, 16), -3, 3, 20,
                                  "relu_sq", 1.0, True, "triton", "no_such_kernel")

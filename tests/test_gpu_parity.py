@@ -126,12 +126,12 @@ def test_backward_stress_distributions(workload, impl):
 
 
 @pytest.mark.parametrize("impl", IMPLS)
-@pytest.mark.parametrize("name", ["uniform", "d20_like", "skewed", "collapsed"])
+@pytest.mark.parametrize("name", ["uniform", "d20_like", "skewed", "collapsed", "gelu"])
 def test_golden_vectors_on_gpu(golden, name, impl):
     """The stored outputs of the reference itself, float32 end to end."""
     c = golden[name]
     lo, hi, G, lam = float(c["meta"][0]), float(c["meta"][1]), int(c["meta"][2]), float(c["meta"][3])
-    act = "relu_sq" if c["meta"][4] == 0 else "identity"
+    act = ("relu_sq", "identity", "gelu")[int(c["meta"][4])]
     z = torch.from_numpy(c["z"]).cuda()
     C = torch.from_numpy(c["C"]).cuda()
     go = torch.from_numpy(c["go"]).cuda()
@@ -154,6 +154,23 @@ def test_golden_vectors_on_gpu(golden, name, impl):
     dz2, dC2, _ = ops.feature_backward(z, C, go[:, h:], lo, hi, G, "identity", lam, with_base=False, impl=impl)
     util.assert_parity("delta dz", dz2, c["delta_dz"], dtype)
     util.assert_parity("delta dC", dC2, c["delta_dC"], dtype)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_gelu_base_path(impl):
+    """activation="gelu" (the exact erf form of F.gelu, as rl_spline_kv_reference.py:81-82) in bf16 at a
+    shape the tcgen05 family takes: base half of f and the g_a * phi'(z) term of dz."""
+    N, h, r, G = 300, 64, 32, 20
+    z, C, go = util.make_inputs(N, h, r, G, torch.bfloat16, seed=5)
+    impl = _impl_or_skip(impl, z, C, G)
+    f = ops.feature_forward(z, C, LO, HI, G, "gelu", 0.5, impl=impl)
+    a_ref, d_ref = util.oracle_forward(z, C, LO, HI, G, "gelu", 0.5)
+    util.assert_parity("phi", f[:, :h], a_ref, torch.bfloat16)
+    util.assert_parity("delta", f[:, h:], d_ref, torch.bfloat16)
+    dz, dC, _ = ops.feature_backward(z, C, go, LO, HI, G, "gelu", 0.5, impl=impl)
+    dz_ref, dC_ref = util.oracle_backward(z, C, go, LO, HI, G, "gelu", 0.5)
+    util.assert_parity("dz", dz, dz_ref, torch.bfloat16)
+    util.assert_parity("dC", dC, dC_ref, torch.bfloat16, bias=True)
 
 
 @pytest.mark.parametrize("impl", IMPLS)

@@ -10,12 +10,12 @@ import pytest
 from oracle import c_binding as oc
 from oracle import spline_kv_oracle as onp
 
-CASES = ["uniform", "d20_like", "skewed", "collapsed", "edges"]
+CASES = ["uniform", "d20_like", "skewed", "collapsed", "edges", "gelu"]
 
 
 def _meta(c):
     lo, hi, G, lam, act, finite = c["meta"]
-    return float(lo), float(hi), int(G), float(lam), ("relu_sq" if act == 0 else "identity"), bool(finite)
+    return float(lo), float(hi), int(G), float(lam), ("relu_sq", "identity", "gelu")[int(act)], bool(finite)
 
 
 def _close(a, b, rtol=2e-5, atol=2e-6):
