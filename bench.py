@@ -10,7 +10,7 @@ pre-activations, with the float32 dC all-reduce over NCCL).  Rank 0 prints one J
 
 * ``value``: tokens/s of all ranks with inputs resident in HBM, CUDA-event timed, max over ranks.
 * ``e2e``: the same through the public operator with HOST buffers: each step copies z and the
-  upstream gradient from pinned host memory and copies f, dz and dC back, pipelined over eight
+  upstream gradient from pinned host memory and copies f, dz and dC back, pipelined over sixteen
   token chunks on three streams so that copies in both directions overlap the kernels.
 * ``roofline``: the slowest of the three main kernels (forward, dz, dC), timed alone with CUDA
   events in a separate pass of the same length, against the measured dense bf16 peak.
@@ -199,7 +199,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--e2e-chunks", type=int, default=8, help="token chunks the end-to-end step is pipelined over")
+    ap.add_argument("--e2e-chunks", type=int, default=16, help="token chunks the end-to-end step is pipelined over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg = make_cfg(args.gpus)
