@@ -125,6 +125,27 @@ class ClockSampler:
                     reasons=sorted(self.reasons), samples=len(self.sm))
 
 
+def bind_to_gpu_numa_node(index: int):
+    """Run this process on the host cores NVML reports as local to its GPU (a read-only query), so
+    that the pinned host buffers of the end-to-end leg are allocated on that GPU's NUMA node.
+    Returns the core list, or None when the query or the binding is not possible."""
+    try:
+        import pynvml as nvml
+        nvml.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = int(vis.split(",")[index]) if vis and vis.split(",")[index].isdigit() else index
+        handle = nvml.nvmlDeviceGetHandleByIndex(idx)
+        words = nvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cores = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cores &= os.sched_getaffinity(0)
+        if not cores:
+            return None
+        os.sched_setaffinity(0, cores)
+        return sorted(cores)
+    except Exception:
+        return None
+
+
 def cpu_port_tokens_per_s(cfg, seed, target_seconds=12.0):
     """Forward + backward of the CPU oracle (C/OpenMP port) on a token sample of the workload."""
     import numpy as np
@@ -222,6 +243,7 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    bind_to_gpu_numa_node(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()

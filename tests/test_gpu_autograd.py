@@ -89,3 +89,43 @@ def test_forced_kernel_names_and_env_override(monkeypatch):
     monkeypatch.setenv("SPARSE_SPLINE_FWD_KERNEL", "bogus")
     with pytest.raises(ValueError):
         skv.flash_spline_feature(z, C, LO, HI, G)
+
+
+def test_forward_backward_under_cuda_graph_capture():
+    """The operator enqueues on the current stream without host synchronisation, so a training step
+    can be captured into a CUDA graph; during capture dC is accumulated into the preallocated
+    ``C.grad`` as the reference does (flash_spline_feature_autograd.py:154-172).  The replayed
+    graph must give the eager results for new input values."""
+    N, h, r = 640, 128, 32
+    z_a, C, go = util.make_inputs(N, h, r, G, torch.bfloat16, seed=11)
+    z_b, _, _ = util.make_inputs(N, h, r, G, torch.bfloat16, seed=12)
+    C.requires_grad_(True)
+    z_static = z_a.clone().requires_grad_(True)
+    # eager warm-up on a side stream (allocates the status word and the caching allocator's blocks)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            f = skv.flash_spline_feature(z_static, C, LO, HI, G, "relu_sq", 0.5, True)
+            f.backward(go)
+    torch.cuda.current_stream().wait_stream(s)
+    z_static.grad.zero_()
+    C.grad.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        f_static = skv.flash_spline_feature(z_static, C, LO, HI, G, "relu_sq", 0.5, True)
+        f_static.backward(go)
+    for z_new in (z_a, z_b):
+        with torch.no_grad():
+            z_static.copy_(z_new)
+            z_static.grad.zero_()
+            C.grad.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        a_ref, d_ref = util.oracle_forward(z_new, C, LO, HI, G, "relu_sq", 0.5)
+        dz_ref, dC_ref = util.oracle_backward(z_new, C, go, LO, HI, G, "relu_sq", 0.5)
+        util.assert_parity("delta", f_static[:, h:], d_ref, torch.bfloat16)
+        util.assert_parity("a", f_static[:, :h], a_ref, torch.bfloat16)
+        util.assert_parity("dz", z_static.grad, dz_ref, torch.bfloat16)
+        util.assert_parity("dC", C.grad, dC_ref, torch.bfloat16)
+    skv.ops.check_status(z_static.device)
