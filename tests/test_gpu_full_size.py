@@ -75,3 +75,28 @@ def test_backward_properties_and_parity(data):
     _, dC2, _ = ops.feature_backward(z, C, go * 2, LO, HI, G, "relu_sq", 0.5, need_dz=False)
     assert torch.equal(dC2, 2 * dC)
     ops.check_status(z.device)
+
+
+@pytest.mark.parametrize("r,G", [(16, 20), (64, 20), (128, 20), (32, 40)], ids=["r16", "r64", "r128", "G40"])
+def test_other_ranks_and_grids_at_full_key_count(r, G):
+    """Code ranks 16 / 64 / 128 at G = 20 and rank 32 at G = 40, all h = 5120 keys wide, on 4096 tokens:
+    forward, dz and dC against the oracle on every token, indices bit for bit, exact zeros."""
+    n = 4096
+    g = torch.Generator(device="cuda").manual_seed(100 + r + G)
+    z = (torch.randn(n, H, generator=g, device="cuda") * 2.0).to(torch.bfloat16)
+    C = (torch.randn(H, G + 2, r, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    go = torch.randn(n, H + r, generator=g, device="cuda").to(torch.bfloat16)
+    assert ops.resolve_impl(z, C, LO, HI, G) == "tcgen05"
+    assert np.array_equal(ops.knot_index(z, LO, HI, G).cpu().numpy(), util.oc.knot_index(util.f32(z), LO, HI, G))
+    f = ops.feature_forward(z, C, LO, HI, G, "relu_sq", 0.25)
+    a_ref, d_ref = util.oracle_forward(z, C, LO, HI, G, "relu_sq", 0.25)
+    util.assert_parity("phi(z)", f[:, :H], a_ref, torch.bfloat16)
+    util.assert_parity("delta", f[:, H:], d_ref, torch.bfloat16)
+    dz, dC, _ = ops.feature_backward(z, C, go, LO, HI, G, "relu_sq", 0.25)
+    dz_ref, dC_ref = util.oracle_backward(z, C, go, LO, HI, G, "relu_sq", 0.25)
+    util.assert_parity("dz", dz, dz_ref, torch.bfloat16)
+    util.assert_parity("dC", dC, dC_ref, torch.bfloat16, bias=True)
+    assert torch.count_nonzero(dC[:, -1, :]) == 0
+    f0 = ops.feature_forward(z, torch.zeros_like(C), LO, HI, G, "relu_sq", 0.25)
+    assert torch.count_nonzero(f0[:, H:]) == 0
+    ops.check_status(z.device)
