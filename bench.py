@@ -11,9 +11,17 @@ pre-activations, with the float32 dC all-reduce over NCCL).  Rank 0 prints one J
 * ``value``: tokens/s of all ranks with inputs resident in HBM, CUDA-event timed, max over ranks.
 * ``e2e``: the same through the public operator with HOST buffers: each step copies z and the
   upstream gradient from pinned host memory and copies f, dz and dC back, pipelined over sixteen
-  token chunks on three streams so that copies in both directions overlap the kernels.
-* ``roofline``: the slowest of the three main kernels (forward, dz, dC), timed alone with CUDA
-  events in a separate pass of the same length, against the measured dense bf16 peak.
+  token chunks on three streams so that copies in both directions overlap the kernels.  It is bound
+  by the host link (PCIe and the host's memory), not by the kernels.
+* ``roofline``: of forward and backward (the dz and dC kernels), the one furthest from its roofline, timed alone with
+  CUDA events in a separate pass of the same length, against the measured dense bf16 peak.
+* ``parity``: after the timed region, the operator against the CPU oracle on a token subset
+  (knot-index mismatches, maxabs(diff)/maxabs(ref) and mean signed error of the float32 residual,
+  dz and dC) and, on more than one GPU, the all-reduced dC against the float64 sum of the ranks'
+  own float32 dC.
+* ``extra``: short bounded measurements of the other configurations: the key-sharded mode at
+  N = 131072 (partial residuals all-reduced), the rank/grid sweep (r = 16, 64, 128 at G = 20 and
+  r = 32 at G = 40) and a stack of 7 layers with their W_in / W_out GEMMs.
 * ``cpu_baseline``: the CPU oracle (a C/OpenMP port of the reference's algorithm) on a bounded
   token sample of the same workload, all host threads.
 
@@ -35,6 +43,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "spline-KV fwd+bwd tokens/s @ h=5120,G=20,r=32 bf16"
 SHAPE = dict(N=65536, d=1280, h=5120, G=20, r=32, grid_lo=-5.0, grid_hi=5.0)
+PARITY_TOKENS = 1024
 
 
 def measured_peaks():
@@ -147,10 +156,13 @@ def bind_to_gpu_numa_node(index: int):
 
 
 def cpu_port_tokens_per_s(cfg, seed, target_seconds=12.0):
-    """Forward + backward of the CPU oracle (C/OpenMP port) on a token sample of the workload."""
+    """Forward + backward of the CPU oracle (C/OpenMP port) on a token sample of the workload, on
+    every host core this process may run on (the thread count is set explicitly: a launcher such as
+    torch.distributed.run exports OMP_NUM_THREADS=1)."""
     import numpy as np
     from oracle import c_binding as oc
     oc.build()
+    oc.set_threads(len(os.sched_getaffinity(0)))
     h, r, G = cfg["h"], cfg["r"], cfg["G"]
     lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
     rng = np.random.default_rng(seed)
@@ -220,6 +232,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the parity and extra-configuration records")
+    ap.add_argument("--fused-backward", action="store_true",
+                    help="run dz and dC as one kernel where its plan fits (A/B against the default two kernels)")
     ap.add_argument("--e2e-chunks", type=int, default=16, help="token chunks the end-to-end step is pipelined over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -248,6 +263,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
     _lib.check(lib.skv_device_ok())
+    if args.fused_backward:
+        lib.skv_debug_set(_lib.SKV_DEBUG_FUSED_BACKWARD, 1)
 
     N, d, h, G, r = cfg["N"], cfg["d"], cfg["h"], cfg["G"], cfg["r"]
     lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
@@ -305,33 +322,44 @@ def main():
     ms_per_step = total_ms / args.steps
     value = world * N / (ms_per_step * 1e-3)
 
-    # ---- per-kernel attribution: forward, dz and dC each timed alone over the same number of steps
+    # ---- per-kernel attribution: forward and backward each timed alone over the same number of steps;
+    # the backward also as its two separate kernels (dz alone, dC alone), which is how it runs where the
+    # fused kernel does not apply
     zd, Cd = z.detach(), C.detach()
     kern = {}
     kern["forward"] = timed(lambda: ops.feature_forward(zd, Cd, lo, hi, G, "relu_sq", lam), args.steps) / args.steps
-    kern["dz"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam, need_dC=False),
-                       args.steps) / args.steps
-    kern["dC"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam, need_dz=False),
-                       args.steps) / args.steps
+    kern["backward"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam),
+                             args.steps) / args.steps
+    kern_split = {}
+    kern_split["dz"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam, need_dC=False),
+                             args.steps) / args.steps
+    kern_split["dC"] = timed(lambda: ops.feature_backward(zd, Cd, go, lo, hi, G, "relu_sq", lam, need_dz=False),
+                             args.steps) / args.steps
     impl = ops.resolve_impl(zd, Cd, lo, hi, G)
     peaks = measured_peaks()
-    dominant = max(kern, key=kern.get)
     flops = 2.0 * N * h * (G + 2) * r                      # dense-equivalent FLOPs of one of the three GEMMs
-    achieved = flops / (kern[dominant] * 1e-3) / 1e12
+    gemms = {"forward": 1, "backward": 2}                  # the backward is the dz and the dC contraction
+    frac_of = {k: gemms[k] * flops / (kern[k] * 1e-3) / 1e12 / peaks["bf16_tflops"] for k in kern}
+    dominant = min(frac_of, key=frac_of.get)               # the kernel furthest from its roofline
+    achieved = gemms[dominant] * flops / (kern[dominant] * 1e-3) / 1e12
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         with open(tpath) as f:
             rec = json.load(f).get(f"{impl}:{dominant}")
         if rec:
-            # captured at a reduced token count; the large streams are per-token, so it scales with N
-            traffic = rec["bytes_per_launch_65536_tokens"] * N / 65536
+            # captured at a reduced token count: the per-token part scales with N, the rest does not
+            traffic = rec["bytes_per_token"] * N + rec["bytes_fixed"]
+    step_tflops = 3 * flops / (ms_per_step * 1e-3) / 1e12
     roofline = dict(bound="tensor", kernel=f"{impl}:{dominant}", achieved=achieved, peak=peaks["bf16_tflops"],
                     unit="TFLOP/s", frac=achieved / peaks["bf16_tflops"], traffic=traffic,
                     peak_source=peaks["source"] + " burst bf16 (kernel timed alone)",
+                    flops_per_launch=gemms[dominant] * flops,
                     kernel_ms={k: round(v, 4) for k, v in kern.items()},
-                    fwd_bwd_frac_of_tensor_roofline=(3 * flops / (ms_per_step * 1e-3) / 1e12)
-                    / peaks["bf16_tflops_sustained"])
+                    kernel_ms_split_backward={k: round(v, 4) for k, v in kern_split.items()},
+                    kernel_frac={k: round(v, 4) for k, v in frac_of.items()},
+                    step_frac_of_burst_peak=step_tflops / peaks["bf16_tflops"],
+                    step_frac_of_sustained_peak=step_tflops / peaks["bf16_tflops_sustained"])
 
     # ---- end to end through the public operator with host buffers
     e2e = None
@@ -401,7 +429,24 @@ def main():
         h2d = zh.numel() * 2 + goh.numel() * 2
         d2h = fh.numel() * 2 + dzh.numel() * 2 + dCh.numel() * 2
         e2e = dict(value=world * N / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
-                   d2h_bytes_per_step=d2h, ms_per_step=e2e_ms, token_chunks=NCH)
+                   d2h_bytes_per_step=d2h, ms_per_step=e2e_ms, token_chunks=NCH,
+                   bound="host link: every rank streams its inputs and outputs through the host's PCIe root and "
+                         "memory, so this figure does not scale with the GPU count; `value` is the device-side one")
+        ops.check_status(dev)
+        del zh, goh, fh, dzh, dCh, zdev, godev
+
+    parity, extra = None, None
+    if not args.no_extra:
+        parity = parity_record(torch, dist, ops, sharded, z, C, go, cfg, rank, world, dev)
+        C.grad = None
+        z.grad = None
+        del go
+        z = z.detach()
+        torch.cuda.empty_cache()
+        extra = dict(
+            key_sharded=extra_key_sharded(torch, dist, ops, sharded, cfg, rank, world, dev, timed),
+            sweep=extra_sweep(torch, ops, cfg, rank, dev, timed),
+            stack7=extra_stack7(torch, dist, sharded, flash_spline_feature, cfg, kern, rank, world, dev, timed))
         ops.check_status(dev)
 
     cpu_baseline = None
@@ -413,11 +458,184 @@ def main():
     if rank == 0:
         line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                     ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
-                    data="synthetic", config=dict(cfg_json(cfg, world), kernels=impl, out_of_grid_fraction=oor),
-                    clocks=clocks, e2e=e2e, gpu_launches=launches, roofline=roofline, cpu_baseline=cpu_baseline)
+                    data="synthetic", config=cfg_json(cfg, world), kernels=impl, out_of_grid_fraction=oor,
+                    clocks=clocks, e2e=e2e, gpu_launches=launches, roofline=roofline, cpu_baseline=cpu_baseline,
+                    parity=parity, extra=extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# -------------------------------------------------------------------------------------------------
+# records taken after the timed region
+# -------------------------------------------------------------------------------------------------
+def _stats(test, ref):
+    """maxabs(diff)/maxabs(ref), mean signed error, and the latter relative to max(1, maxabs(ref))."""
+    import numpy as np
+    t = np.asarray(test, dtype=np.float64)
+    r = np.asarray(ref, dtype=np.float64)
+    ref_max = float(np.abs(r).max())
+    d = t - r
+    bias = float(d.mean())
+    return dict(rel=float(np.abs(d).max() / max(ref_max, 1e-30)), mean_signed=bias,
+                mean_signed_rel=bias / max(1.0, ref_max), ref_max=ref_max)
+
+
+def parity_record(torch, dist, ops, sharded, z, C, go, cfg, rank, world, dev):
+    """The operator against the CPU oracle on the first PARITY_TOKENS tokens of this rank's batch;
+    on more than one GPU also the collective: the all-reduced dC against the float64 sum of the
+    all-gathered per-rank float32 dC.  Gates: 0 index mismatches, rel <= 1e-2, |mean signed| <= 5e-6
+    (relative to maxabs(ref) where that exceeds 1)."""
+    import numpy as np
+    from oracle import c_binding as oc
+    oc.build()
+    oc.set_threads(len(os.sched_getaffinity(0)))
+    h, G, r = cfg["h"], cfg["G"], cfg["r"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    n = min(PARITY_TOKENS, z.shape[0])
+    zs, gos, Cd = z.detach()[:n], go[:n], C.detach()
+    z32, C32, go32 = zs.float().cpu().numpy(), Cd.float().cpu().numpy(), gos.float().cpu().numpy()
+    bins = ops.knot_index(zs, lo, hi, G).cpu().numpy()
+    mism = int((bins != oc.knot_index(z32, lo, hi, G)).sum())
+    _, d32 = ops.feature_forward(zs, Cd, lo, hi, G, "relu_sq", lam, delta_f32=True)
+    dz, dC32, _ = ops.feature_backward(zs, Cd, gos, lo, hi, G, "relu_sq", lam)
+    _, d_ref = oc.feature_forward(z32, C32, lo, hi, G, "relu_sq", lam)
+    dz_ref, dC_ref = oc.feature_backward(z32, C32, go32[:, h:], go32[:, :h], lo, hi, G, "relu_sq", lam)
+    rec = dict(tokens=n, knot_index_mismatches=mism, delta_f32=_stats(d32.cpu().numpy(), d_ref),
+               dz=_stats(dz.float().cpu().numpy(), dz_ref), dC_f32=_stats(dC32.cpu().numpy(), dC_ref))
+    ok = mism == 0 and all(rec[k]["rel"] <= 1e-2 for k in ("delta_f32", "dz", "dC_f32")) and all(
+        abs(rec[k]["mean_signed_rel"]) <= 5e-6 for k in ("delta_f32", "dC_f32"))
+    if world > 1:
+        # every rank's own dC of its whole batch, gathered, summed in float64, against the operator's
+        # all-reduced result
+        _, mine, _ = ops.feature_backward(z.detach(), Cd, go, lo, hi, G, "relu_sq", lam, need_dz=False)
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        total = torch.zeros_like(mine, dtype=torch.float64)
+        for p in parts:
+            total += p.double()
+        zz = z.detach().requires_grad_(False)
+        Cg = Cd.clone().requires_grad_(True)
+        f = sharded.token_sharded_spline_feature(zz, Cg, lo, hi, G, "relu_sq", lam)
+        f.backward(go)
+        diff = (Cg.grad.double() - total).abs().max().item()
+        ref_max = total.abs().max().item()
+        rec["allreduced_dC_vs_f64_sum_of_ranks"] = dict(rel=diff / max(ref_max, 1e-30), ref_max=ref_max,
+                                                        ranks=world, rounding="result is bf16 (dtype of C)")
+        ok = ok and diff <= 1e-2 * ref_max
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ok = bool(flag.item())
+    rec["within_gates_on_all_ranks"] = ok
+    return rec
+
+
+def extra_key_sharded(torch, dist, ops, sharded, cfg, rank, world, dev, timed, N=131072, steps=5):
+    """The key-sharded mode at the rank/grid sweep's token count: every rank holds all N tokens and
+    h / P keys; the partial residuals are all-reduced in float32.  Timing of forward + backward, and
+    the all-reduced residual against the unsharded operator on a replicated 2048-token subset."""
+    h, G, r = cfg["h"], cfg["G"], cfg["r"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    ks = sharded.key_slice(h, world, rank, multiple=16)
+    hl = ks.stop - ks.start
+    cgen = torch.Generator(device=dev).manual_seed(4242)         # replicated tensors: same seed on all ranks
+    C = (torch.randn(h, G + 2, r, generator=cgen, device=dev) * 0.02).to(torch.bfloat16)
+    zsub = (torch.randn(2048, h, generator=cgen, device=dev) * cfg["z_std"]).to(torch.bfloat16)
+    _, d_full = ops.feature_forward(zsub, C, lo, hi, G, "relu_sq", lam, delta_f32=True)
+    _, d_sh = sharded.key_sharded_spline_feature(zsub[:, ks].contiguous(), C[ks].contiguous(), lo, hi, G, "relu_sq", lam)
+    dmax = d_full.abs().max().item()
+    rel = (d_sh.float() - d_full).abs().max().item() / max(dmax, 1e-30)
+    gen = torch.Generator(device=dev).manual_seed(77 + rank)
+    zl = (torch.randn(N, hl, generator=gen, device=dev) * cfg["z_std"]).to(torch.bfloat16).requires_grad_(True)
+    Cl = C[ks].contiguous().requires_grad_(True)
+    ga = torch.randn(N, hl, generator=gen, device=dev).to(torch.bfloat16)
+    gd = torch.randn(N, r, generator=cgen, device=dev).to(torch.bfloat16)
+
+    def step():
+        zl.grad = None
+        Cl.grad = None
+        a, delta = sharded.key_sharded_spline_feature(zl, Cl, lo, hi, G, "relu_sq", lam)
+        torch.autograd.backward([a, delta], [ga, gd])
+
+    for _ in range(3):
+        step()
+    ms = timed(step, steps) / steps
+    return dict(workload=f"key-sharded, N={N} tokens on every rank, {hl} of {h} keys per rank, r={r}, G={G} (config 4)",
+                ms_per_step=ms, tokens_per_s=N / (ms * 1e-3), steps=steps,
+                allreduced_delta_vs_unsharded=dict(rel=rel, ref_max=dmax, tokens=2048,
+                                                   rounding="sharded result is bf16"),
+                within_gate=rel <= 1e-2)
+
+
+def extra_sweep(torch, ops, cfg, rank, dev, timed, N=131072, steps=5):
+    """Kernel times of the rank/grid sweep at h = 5120, N = 131072 on this GPU: r = 16, 64, 128 at
+    G = 20 and r = 32 at G = 40 (config 4; its token-sharded form is this on every rank)."""
+    h = cfg["h"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    gen = torch.Generator(device=dev).manual_seed(555 + rank)
+    z = (torch.randn(N, h, generator=gen, device=dev) * cfg["z_std"]).to(torch.bfloat16)
+    out = []
+    for r, G in ((16, 20), (64, 20), (128, 20), (32, 40)):
+        C = (torch.randn(h, G + 2, r, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+        go = torch.randn(N, h + r, generator=gen, device=dev).to(torch.bfloat16)
+        fwd = lambda: ops.feature_forward(z, C, lo, hi, G, "relu_sq", lam)
+        bwd = lambda: ops.feature_backward(z, C, go, lo, hi, G, "relu_sq", lam)
+        for _ in range(2):
+            fwd()
+            bwd()
+        f_ms = timed(fwd, steps) / steps
+        b_ms = timed(bwd, steps) / steps
+        flops = 2.0 * N * h * (G + 2) * r
+        out.append(dict(r=r, G=G, N=N, forward_ms=round(f_ms, 4), backward_ms=round(b_ms, 4),
+                        tokens_per_s=N / ((f_ms + b_ms) * 1e-3),
+                        dense_equiv_tflops=round(3 * flops / ((f_ms + b_ms) * 1e-3) / 1e12, 1)))
+        del C, go
+    return out
+
+
+def extra_stack7(torch, dist, sharded, flash_spline_feature, cfg, kern, rank, world, dev, timed, layers=7, steps=3):
+    """Seven consecutive layers x -> z = x W_in -> f = feature(z, C) -> y = f W_out^T, x <- x + y at
+    the d20 shape (config 3), forward then backward through all of them, N = 65536 tokens per GPU;
+    the GEMMs are torch (cuBLAS) bf16 matmuls, the operator is this library's; on more than one GPU
+    every layer's dC is all-reduced by the token-sharded operator and the W gradients in one call."""
+    N, d, h, G, r = cfg["N"], cfg["d"], cfg["h"], cfg["G"], cfg["r"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    wgen = torch.Generator(device=dev).manual_seed(31337)         # weights are replicated
+    gen = torch.Generator(device=dev).manual_seed(9 + rank)
+    bf = torch.bfloat16
+    W_in = [(torch.randn(d, h, generator=wgen, device=dev) / d ** 0.5).to(bf).requires_grad_(True) for _ in range(layers)]
+    # small read-out weights keep the residual stream (there is no normalisation in this stack) inside the grid
+    W_out = [(torch.randn(h + r, d, generator=wgen, device=dev) * 0.05 / (h + r) ** 0.5).to(bf).requires_grad_(True)
+             for _ in range(layers)]
+    Cs = [(torch.randn(h, G + 2, r, generator=wgen, device=dev) * 0.02).to(bf).requires_grad_(True) for _ in range(layers)]
+    x0 = (torch.randn(N, d, generator=gen, device=dev) * cfg["z_std"]).to(bf)
+    gy = torch.randn(N, d, generator=gen, device=dev).to(bf)
+    params = W_in + W_out + Cs
+
+    def step():
+        for p in params:
+            p.grad = None
+        x = x0
+        for l in range(layers):
+            z = x @ W_in[l]
+            if world == 1:
+                f = flash_spline_feature(z, Cs[l], lo, hi, G, "relu_sq", lam, True)
+            else:
+                f = sharded.token_sharded_spline_feature(z, Cs[l], lo, hi, G, "relu_sq", lam)
+            x = x + f @ W_out[l]
+        x.backward(gy)
+        if world > 1:
+            flat = torch.cat([w.grad.reshape(-1) for w in W_in + W_out]).float()
+            dist.all_reduce(flat)
+
+    for _ in range(2):
+        step()
+    ms = timed(step, steps) / steps
+    op_ms = layers * (kern["forward"] + kern["backward"])
+    return dict(workload=f"{layers} layers with W_in [d,h] and W_out [h+r,d] GEMMs, N={N} tokens per GPU (config 3)",
+                ms_per_step=ms, tokens_per_s=world * N / (ms * 1e-3), steps=steps,
+                operator_ms=round(op_ms, 3), operator_share=round(op_ms / ms, 3),
+                note="operator_ms = layers x (forward + backward kernel time measured alone above)")
 
 
 if __name__ == "__main__":

@@ -144,6 +144,21 @@ int skv_feature_forward_noalloc(const skv_problem *p, const void *z, int64_t z_s
                                 void *act_out, int64_t act_stride, void *delta_out, int64_t delta_stride,
                                 int32_t *status, void *stream);
 
+/* Debug and test settings; no counterpart in the reference (whose kernels wait on their barriers
+ * without a limit, src/sparsespline_ffn/cuda_ext/spline_kv_bwd_v6.cu:159-172).  Process-wide, read when a
+ * kernel is launched.
+ *   SKV_DEBUG_WAIT_CYCLES      limit of every bounded device-side wait, in SM clock cycles
+ *                              (default 4e9, about two seconds); a wait that runs out sets a bit
+ *                              in the caller's status word and the kernel returns by itself
+ *   SKV_DEBUG_SKIP_FIRST_COPY  1: the forward's loader leaves out its first code-table copy, so
+ *                              that a wait runs out although nothing is in flight (tests of the
+ *                              time-out path); 0 restores normal operation
+ *   SKV_DEBUG_FUSED_BACKWARD   1: run dz and dC as one kernel (dedicated warps per role in one
+ *                              CTA) where its plan fits, instead of the two kernels used by
+ *                              default; same results, measured no faster (A/B timing, tests) */
+enum skv_debug { SKV_DEBUG_WAIT_CYCLES = 0, SKV_DEBUG_SKIP_FIRST_COPY = 1, SKV_DEBUG_FUSED_BACKWARD = 2 };
+int skv_debug_set(int what, int64_t value);
+
 /* Number of kernels this library has launched in this process so far (host-side counter).  No
  * counterpart in the reference; benchmarks use the difference around a timed region to report
  * how many of the library's own kernels ran inside it. */

@@ -39,6 +39,8 @@ def lib() -> ctypes.CDLL:
         ip = ctypes.POINTER(ctypes.c_int32)
         i64, i32, f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_float
         L.skvo_num_threads.restype = ctypes.c_int
+        L.skvo_set_threads.argtypes = [ctypes.c_int]
+        L.skvo_set_threads.restype = None
         L.skvo_knot_index.argtypes = [fp, i64, i64, i32, f32, f32, i32, ip]
         L.skvo_knot_index.restype = None
         L.skvo_forward.argtypes = [fp, i64, fp, i64, i32, i32, i32, f32, f32, f32, i32, fp, fp]
@@ -67,6 +69,13 @@ _ACT = {"relu_sq": 0, "identity": 1, "gelu": 2}
 
 def num_threads() -> int:
     return int(lib().skvo_num_threads())
+
+
+def set_threads(n: int) -> int:
+    """Use ``n`` OpenMP threads from now on (launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1, which would otherwise make this a one-core baseline); returns the count."""
+    lib().skvo_set_threads(int(n))
+    return num_threads()
 
 
 def knot_index(z32, grid_lo, grid_hi, G) -> np.ndarray:

@@ -72,6 +72,16 @@ int skvo_num_threads(void)
 #endif
 }
 
+/* Number of OpenMP threads the next calls use (a launcher may have exported OMP_NUM_THREADS=1). */
+void skvo_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* bins[N*h] (int32), row-major; z has row stride zs (elements). */
 void skvo_knot_index(const float *z, int64_t zs, int64_t N, int h,
                      float lo, float scale, int G, int32_t *bins)

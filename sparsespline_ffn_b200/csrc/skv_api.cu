@@ -10,6 +10,16 @@ using namespace skv;
 namespace skv {
 static std::atomic<uint64_t> g_launches{0};
 void note_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// Debug / test settings (skv_debug_set), read by the launch code of the tensor-core kernels.
+static std::atomic<long long> g_wait_cycles{4000000000LL};
+static std::atomic<int> g_skip_copy{0};
+static std::atomic<int> g_fused_bwd{0};
+namespace tc {
+long long wait_cycle_limit() { return g_wait_cycles.load(std::memory_order_relaxed); }
+int debug_skip_copy() { return g_skip_copy.load(std::memory_order_relaxed); }
+bool fused_backward_enabled() { return g_fused_bwd.load(std::memory_order_relaxed) != 0; }
+}  // namespace tc
 }  // namespace skv
 
 namespace {
@@ -102,6 +112,23 @@ const char* skv_error_string(int code) {
 }
 
 int skv_device_ok(void) { return device_info(nullptr); }
+
+int skv_debug_set(int what, int64_t value) {
+  switch (what) {
+    case SKV_DEBUG_WAIT_CYCLES:
+      if (value < 1000) return SKV_ERR_UNSUPPORTED;
+      skv::g_wait_cycles.store((long long)value, std::memory_order_relaxed);
+      return SKV_OK;
+    case SKV_DEBUG_SKIP_FIRST_COPY:
+      skv::g_skip_copy.store(value != 0, std::memory_order_relaxed);
+      return SKV_OK;
+    case SKV_DEBUG_FUSED_BACKWARD:
+      skv::g_fused_bwd.store(value != 0, std::memory_order_relaxed);
+      return SKV_OK;
+    default:
+      return SKV_ERR_UNSUPPORTED;
+  }
+}
 
 int skv_resolve_impl(const skv_problem* p) {
   if (int e = validate(p)) return e;

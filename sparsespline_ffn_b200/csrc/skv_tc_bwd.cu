@@ -138,6 +138,7 @@ struct DzParams {
   int chunks_total, chunks_per_split;
   int tstages;               // depth of the transformed-table ring (2..kTStages)
   int32_t* status;
+  long long wait_cycles;     // limit of every bounded wait, in clock cycles
 };
 
 
@@ -218,8 +219,10 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
   uint64_t* tempty = tfull + kTStages;       // [kTStages]
   uint64_t* sfull = tempty + kTStages;       // [GROUPS]  MMA -> consumers
   uint64_t* sempty = sfull + GROUPS;         // [GROUPS]  consumers -> MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty + GROUPS);
+  uint64_t* done = sempty + GROUPS;          // [1]       all MMAs of this CTA complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wc{abort_flag, P.status, kStatusTimeoutDz, P.wait_cycles};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk_begin = blockIdx.y * P.chunks_per_split;
@@ -232,6 +235,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
     mbar_init(gfull, 1);
     for (int i = 0; i < kTStages; ++i) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 1); }
     for (int i = 0; i < GROUPS; ++i) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 128); }
+    mbar_init(done, 1);
     *abort_flag = 0;
     mbar_init_fence();
   }
@@ -270,7 +274,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       const uint32_t gw[4] = {gac.x, gac.y, gac.z, gac.w};
       uint32_t bufa[LB][8], bufb[LB][8];
       float outv[kChunkKeys];
-      mbar_wait(sfull + grp, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutDz);
+      mbar_wait(sfull + grp, (uint32_t)ci & 1u, wc);
       tc_fence_after();
       tmem_ld_key<LB>(trow, bufa);
 #pragma unroll
@@ -305,15 +309,16 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
   } else if (warp == 4 * GROUPS) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      mbar_wait(gfull, 0, abort_flag, P.status, kStatusTimeoutDz);
+      mbar_wait(gfull, 0, wc);
       const uint32_t rb = (uint32_t)(r / 8) * 128u;          // bytes between 8-row groups of the T image
       const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % TS;
-        mbar_wait(tfull + s, (uint32_t)(ci / TS) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+        mbar_wait(tfull + s, (uint32_t)(ci / TS) & 1u, wc);
         const uint32_t b_addr = smem_u32(t_base + (size_t)s * t_bytes);
         for (int grp = 0; grp < GROUPS; ++grp) {
-          if (ci > 0) mbar_wait(sempty + grp, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+          if (ci > 0) mbar_wait(sempty + grp, (uint32_t)(ci - 1) & 1u, wc);
+          if (*abort_flag) break;                    // draining: issue nothing more
           tc_fence_after();
           const uint32_t a_lo0 = desc_lo(smem_u32(g_base + (size_t)grp * g_bytes), 2048u);
           for (uint32_t c0 = 0; c0 < ncols; c0 += 256) {
@@ -330,8 +335,10 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
           }
           umma_commit(sfull + grp);
         }
+        if (*abort_flag) break;
         umma_commit(tempty + s);
       }
+      umma_commit(done);
     }
   } else {
     // ------------------------------------------------------------------ loader
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % TS;
         if (ci >= TS)
-          mbar_wait(tempty + s, (uint32_t)((ci / TS) - 1) & 1u, abort_flag, P.status, kStatusTimeoutDz);
+          mbar_wait(tempty + s, (uint32_t)((ci / TS) - 1) & 1u, wc);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(tfull + s, t_bytes);
         bulk_g2s(t_base + (size_t)s * t_bytes, src + (size_t)ci * t_bytes, t_bytes, tfull + s);
@@ -359,6 +366,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
   tc_fence_before();
   __syncthreads();
   if (warp == 4 * GROUPS) {
+    mbar_wait_drain(done, 0, P.wait_cycles);
     tc_fence_after();
     tmem_free(tmem_base, tmem_cols);
   }
@@ -381,6 +389,7 @@ struct DcParams {
   int64_t tiles_per_split;   // 128-token tiles per token split
   int64_t tiles_total;
   int32_t* status;
+  long long wait_cycles;     // limit of every bounded wait, in clock cycles
 };
 
 // KCH = keys per chunk.  Two producer groups of 128 threads (thread = token of the group's tile).
@@ -400,6 +409,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
   uint64_t* done = gempty + 2;     // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wc{abort_flag, P.status, kStatusTimeoutDc, P.wait_cycles};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rows = KCH * L;                                          // knot rows per chunk
@@ -463,7 +473,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
           znext[i] = valid && in_h ? __ldg(reinterpret_cast<const uint4*>(zrow + (ch + 1) * KCH + i * 8))
                                    : make_uint4(0, 0, 0, 0);
         }
-        if (use > 0) mbar_wait(pempty + pg, (uint32_t)(use - 1) & 1u, abort_flag, P.status, kStatusTimeoutDc);
+        if (use > 0) mbar_wait(pempty + pg, (uint32_t)(use - 1) & 1u, wc);
         if (have_saved) {
 #pragma unroll
           for (int q = 0; q < KCH; ++q) {
@@ -494,7 +504,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
       }
     }
     // ---- epilogue: accumulators -> float32 partial of this token split
-    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutDc);
+    mbar_wait(done, 0, wc);
     tc_fence_after();
     const int lane_row = (warp & 3) * 32 + lane;
     float* part = P.part + (size_t)blockIdx.y * P.h * L * r;
@@ -526,11 +536,12 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
       for (int tp = 0; tp < ntiles; tp += 2) {
         const int npg = min(2, ntiles - tp);
         for (int pg = 0; pg < npg; ++pg)
-          mbar_wait(gfull + pg, (uint32_t)guse[pg] & 1u, abort_flag, P.status, kStatusTimeoutDc);
+          mbar_wait(gfull + pg, (uint32_t)guse[pg] & 1u, wc);
         for (int ch = 0; ch < nchunks; ++ch) {
           for (int pg = 0; pg < npg; ++pg) {
-            mbar_wait(pfull + pg, (uint32_t)puse[pg] & 1u, abort_flag, P.status, kStatusTimeoutDc);
+            mbar_wait(pfull + pg, (uint32_t)puse[pg] & 1u, wc);
             ++puse[pg];
+            if (*abort_flag) break;                  // draining: issue nothing more
             tc_fence_after();
             const uint32_t a_addr = smem_u32(phi_base + (size_t)pg * phi_bytes);
             const uint32_t b_addr = smem_u32(g_base + (size_t)pg * g_bytes);
@@ -550,7 +561,9 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
             }
             umma_commit(pempty + pg);
           }
+          if (*abort_flag) break;
         }
+        if (*abort_flag) break;
         for (int pg = 0; pg < npg; ++pg) { umma_commit(gempty + pg); ++guse[pg]; }
       }
       umma_commit(done);
@@ -562,7 +575,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
       for (int ti = 0; ti < ntiles; ++ti) {
         const int pg = ti & 1;
         if (guse[pg] > 0)
-          mbar_wait(gempty + pg, (uint32_t)(guse[pg] - 1) & 1u, abort_flag, P.status, kStatusTimeoutDc);
+          mbar_wait(gempty + pg, (uint32_t)(guse[pg] - 1) & 1u, wc);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(gfull + pg, g_bytes);
         bulk_g2s(g_base + (size_t)pg * g_bytes,
@@ -577,7 +590,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
   }
   __syncthreads();
   if (warp == 8) {
-    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutDc);
+    mbar_wait_drain(done, 0, P.wait_cycles);
     tc_fence_after();
     tmem_free(tmem_base, tmem_cols);
   }
@@ -595,6 +608,409 @@ __global__ void tc_dc_reduce_kernel(const float* __restrict__ part, int splits, 
     s *= f;
     if (dC) dC[i] = s;
     if (dC_cast) dC_cast[i] = __float2bfloat16_rn(s);
+  }
+}
+
+// =================================================================================================
+// fused backward: dz and dC in one CTA
+// =================================================================================================
+// A CTA owns a slab of 16 keys and a range of 128-token tiles; tile i belongs to token group i % 2.
+// The dz kernel is bound by instruction issue and the dC kernel by shared-memory bandwidth (its
+// producers wait half the time for the MMAs that read their stage); run as separate warps of one
+// CTA the two fill each other's gaps, and the g tile in shared memory serves both.
+//
+//   warps 0..7    dz role, groups 0 and 1 (thread = token): the S columns of 4 keys at a time
+//                 (S = g T^T, in one of the group's two tensor-memory blocks, so that the next
+//                 block is computed while this one is read) -> dz, as tc_dz_kernel does
+//   warps 8..15   Phi role, groups 0 and 1: a group fills stages of 64 tokens x 16 keys (two
+//                 threads per token, 8 keys each): knot interval and weights -> the two non-zero
+//                 words of each key's Phi^T segment, scattered into the stage (A operand of the dC
+//                 MMAs); two stages per group, so that one is filled while the other is read
+//   warp 16       lane 0 issues the S MMAs of both groups (whichever is ready first)
+//   warp 17       lane 0 issues the dC MMAs of both groups (3 M-tiles x 4 K-steps per stage)
+//   warp 18       lane 0 loads the slab's transformed table once and streams the g tiles (3-deep ring)
+//
+// Registers are re-balanced between the roles with setmaxnreg (the kernel starts every warp with
+// the same count): the helper warps give registers up, the dz warps take them.
+//
+// Tensor memory: [group 0: S block 0, S block 1 | group 1: ... | dC accumulators of the slab]
+// = 4 * 4*LP + mtiles*r columns.
+// Shared memory: four Phi^T stages of 16*L knot rows x 64 tokens, the g ring, the table slab.  A
+// stage holds exactly 16*L rows; the MMAs of its last M-tile read up to the next multiple of 128
+// rows, i.e. into whatever follows the stage.  Each accumulator row depends on its own A row only
+// and the rows past 16*L are never stored, so those reads are harmless.
+struct BfParams {
+  const __nv_bfloat16* z;
+  int64_t zs;
+  const __nv_bfloat16* g_act;
+  int64_t gas;
+  __nv_bfloat16* dz;
+  int64_t dzs;
+  const __half* gimg;
+  const __half* timg;
+  const uint32_t* amax_bits;
+  float* part;               // [splits][h*L][r]
+  int64_t N;
+  int h, L, r;
+  GridParams g;
+  int act;
+  float coef;                // lambda * scale
+  int mtiles;                // 128-row MMA tiles over the slab's 16*L knot rows
+  int64_t tiles_per_split, tiles_total;
+  int32_t* status;
+  long long wait_cycles;
+};
+
+constexpr int kSlabKeys = 16;
+constexpr int kGRing = 3;
+constexpr int kBfThreads = 640;
+// register counts per role (multiples of 8); 256 * kRegsDz + 256 * kRegsPhi + 128 * kRegsAux must
+// not exceed kBfThreads * the count the kernel is compiled for (96)
+constexpr int kRegsDz = 128, kRegsPhi = 88, kRegsAux = 40;
+#ifndef SKV_POLL_NS
+#define SKV_POLL_NS 20
+#endif
+constexpr unsigned kPollNs = SKV_POLL_NS;               // pause of an MMA issuer that found nothing ready
+
+template <int R> __device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
+}
+template <int R> __device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
+}
+
+template <int LB, int NC, bool RELU>
+__global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int L = P.L, r = P.r;
+  constexpr int LP = 8 * LB;
+  constexpr uint32_t bcols = (uint32_t)(4 * LP);                    // columns of one S block (4 keys)
+  const uint32_t phi_bytes = (uint32_t)((kSlabKeys * L + 7) / 8) * 1024u;   // one 64-token stage
+  const uint32_t g_bytes = (uint32_t)(128 * r * 2);
+  const uint32_t t_bytes = (uint32_t)(kChunkKeys * LP * r * 2);     // table image of 8 keys
+  uint8_t* phi_base = smem;                                          // [2 groups][2][phi_bytes]
+  uint8_t* g_base = phi_base + 4 * (size_t)phi_bytes;                // [kGRing][g_bytes]
+  uint8_t* t_base = g_base + (size_t)kGRing * g_bytes;               // [2][t_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(t_base + 2 * (size_t)t_bytes);
+  uint64_t* gfull = bars;                  // [kGRing] loader -> MMA issuers
+  uint64_t* gempty = gfull + kGRing;       // [kGRing] both MMA issuers -> loader (2 arrivals)
+  uint64_t* tfull = gempty + kGRing;       // [1]
+  uint64_t* sfull = tfull + 1;             // [2 groups][2] S issuer -> dz group
+  uint64_t* sempty = sfull + 4;            // [2 groups][2] dz group -> S issuer
+  uint64_t* pfull = sempty + 4;            // [2 groups][2] Phi group -> dC issuer
+  uint64_t* pempty = pfull + 4;            // [2 groups][2] dC issuer -> Phi group
+  uint64_t* done = pempty + 4;             // [2] all MMAs of the S issuer / the dC issuer complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wc{abort_flag, P.status, kStatusTimeoutBwd, P.wait_cycles};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int key0 = blockIdx.x * kSlabKeys;
+  const int64_t tile_begin = (int64_t)blockIdx.y * P.tiles_per_split;
+  const int ntiles = (int)min(P.tiles_per_split, P.tiles_total - tile_begin);
+  const uint32_t dcol0 = 4u * bcols;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < dcol0 + (uint32_t)(P.mtiles * r)) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int i = 0; i < kGRing; ++i) { mbar_init(gfull + i, 1); mbar_init(gempty + i, 2); }
+    mbar_init(tfull, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(sfull + i, 1);
+      mbar_init(sempty + i, 128);
+      mbar_init(pfull + i, 128);
+      mbar_init(pempty + i, 1);
+    }
+    mbar_init(done + 0, 1);
+    mbar_init(done + 1, 1);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  {
+    uint4* p = reinterpret_cast<uint4*>(phi_base);
+    const uint32_t n16 = 4 * phi_bytes / 16;
+    for (uint32_t i = tid; i < n16; i += blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (warp == 16) tmem_alloc(tmem_slot, tmem_cols);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ dz role
+    reg_inc<kRegsDz>();
+    const int pg = warp >> 2;
+    const int t = tid & 127;
+    const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)pg * 2u * bcols;
+    float gscale, ginv;
+    g_scales(*P.amax_bits, gscale, ginv);
+    const float coef = P.coef * ginv;
+    const int act = P.act;
+    const bool has_ga = P.g_act != nullptr;
+    auto load_rows = [&](int ti, uint4 (&zv)[2], uint4 (&gv)[2], bool& valid, __nv_bfloat16*& dzrow) {
+      const int64_t n = (tile_begin + ti) * 128 + t;
+      valid = ti < ntiles && n < P.N;
+      const int64_t nn = valid ? n : 0;
+      const __nv_bfloat16* zrow = P.z + nn * P.zs + key0;
+      const __nv_bfloat16* garow = has_ga ? P.g_act + nn * P.gas + key0 : nullptr;
+      dzrow = P.dz + nn * P.dzs + key0;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        zv[i] = valid ? __ldg(reinterpret_cast<const uint4*>(zrow + i * 8)) : make_uint4(0, 0, 0, 0);
+        gv[i] = valid && has_ga ? __ldg(reinterpret_cast<const uint4*>(garow + i * 8)) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    uint4 znext[2], ganext[2];
+    bool vnext;
+    __nv_bfloat16* dznext;
+    load_rows(pg, znext, ganext, vnext, dznext);
+    int use = 0;                                     // S blocks this group has consumed
+    uint32_t keep0 = 0u, keep1 = 0u;                 // outputs of the even block until the odd one is done
+    for (int ti = pg; ti < ntiles; ti += 2) {
+      const uint4 zq[2] = {znext[0], znext[1]}, gaq[2] = {ganext[0], ganext[1]};
+      const bool valid = vnext;
+      __nv_bfloat16* dzrow = dznext;
+      load_rows(ti + 2, znext, ganext, vnext, dznext);   // the group's next tile: request its rows now
+#pragma unroll 1
+      for (int bk = 0; bk < 4; ++bk, ++use) {            // four S blocks of 4 keys; small body on purpose:
+        // this loop shares the instruction cache of its SM sub-partition with the Phi role's loop
+        const uint4 zc = (bk & 2) ? zq[1] : zq[0], gc = (bk & 2) ? gaq[1] : gaq[0];
+        const uint32_t zw[2] = {(bk & 1) ? zc.z : zc.x, (bk & 1) ? zc.w : zc.y};
+        const uint32_t gw[2] = {(bk & 1) ? gc.z : gc.x, (bk & 1) ? gc.w : gc.y};
+        const uint32_t blk = trow + (uint32_t)(use & 1) * bcols;
+        uint32_t bufa[LB][8], bufb[LB][8];
+        float outv[4];
+        mbar_wait(sfull + pg * 2 + (use & 1), (uint32_t)(use >> 1) & 1u, wc);
+        tc_fence_after();
+        tmem_ld_key<LB>(blk, bufa);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (q & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
+          if (q + 1 < 4) {
+            if (q & 1) tmem_ld_key<LB>(blk + (uint32_t)((q + 1) * LP), bufa);
+            else tmem_ld_key<LB>(blk + (uint32_t)((q + 1) * LP), bufb);
+          }
+          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+          const float u = __fmaf_rn(__fsub_rn(zz, P.g.lo), P.g.scale, 0.0f);
+          const bool active = __float_as_uint(u) <= __float_as_uint(P.g.Gm1f);
+          const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
+          const float acc = (q & 1) ? dz_key_sum<LB, NC>(bufb, uc) : dz_key_sum<LB, NC>(bufa, uc);
+          float o = active ? coef * acc : 0.0f;
+          if (has_ga) {
+            const float ga = (q & 1) ? bf_hi(gw[q >> 1]) : bf_lo(gw[q >> 1]);
+            const float dphi = RELU ? 2.0f * fmaxf(zz, 0.0f) : act_grad(zz, act);
+            o = fmaf(ga, dphi, o);
+          }
+          outv[q] = o;
+        }
+        tc_fence_before();
+        mbar_arrive(sempty + pg * 2 + (use & 1));
+        const uint32_t o01 = pack_bf2(outv[0], outv[1]), o23 = pack_bf2(outv[2], outv[3]);
+        if (bk & 1) {
+          if (valid) *reinterpret_cast<uint4*>(dzrow + (bk - 1) * 4) = make_uint4(keep0, keep1, o01, o23);
+        } else {
+          keep0 = o01;
+          keep1 = o23;
+        }
+      }
+    }
+    // ---- epilogue: the slab's accumulators -> float32 partial of this token split
+    mbar_wait(done + 1, 0, wc);
+    tc_fence_after();
+    const int lane_row = (warp & 3) * 32 + lane;
+    const int rows = kSlabKeys * L;
+    float* part = P.part + ((size_t)blockIdx.y * P.h + key0) * L * r;
+    for (int mt = pg; mt < P.mtiles; mt += 2) {
+      const int rr = mt * 128 + lane_row;
+      const bool ok = rr < rows;
+      float* dst = part + (size_t)rr * r;
+      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + dcol0 + (uint32_t)(mt * r);
+      for (int c0 = 0; c0 < r; c0 += 16) {
+        float v[16];
+        tmem_ld16(taddr + c0, v);
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<float4*>(dst + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp < 16) {
+    // ------------------------------------------------------------------ Phi role
+    reg_dec<kRegsPhi>();
+    const int pg = (warp - 8) >> 2;
+    const int t = tid & 127;
+    const int tok = t & 63, kh = t >> 6;             // token of the half tile, key half of the slab
+    const uint32_t t_off = (uint32_t)(tok & 7) * 16u + (uint32_t)(tok >> 3) * 128u;
+    const uint32_t row0 = smem_u32(phi_base + (size_t)(pg * 2) * phi_bytes) + t_off;
+    const uint32_t halfL = (uint32_t)L >> 1;
+    // first word index (< 16 * L / 2 <= 255) of the pair each key wrote, per stage: 8 keys x 8 bits
+    // in two registers; the positions are cleared before the stage is filled again
+    uint32_t sav[2][2] = {{0u, 0u}, {0u, 0u}};
+    // fill f of this group: tile pg + 2 * (f / 2), token half f % 2, stage f % 2
+    const int nfill = 2 * ((ntiles - pg + 1) / 2);
+    auto load_z = [&](int f, uint4& zv, bool& valid) {
+      const int ti = pg + 2 * (f >> 1);
+      const int64_t n = (tile_begin + ti) * 128 + (f & 1) * 64 + tok;
+      valid = f < nfill && n < P.N;
+      zv = valid ? __ldg(reinterpret_cast<const uint4*>(P.z + n * P.zs + key0 + kh * 8)) : make_uint4(0, 0, 0, 0);
+    };
+    uint4 znext;
+    bool vnext;
+    load_z(0, znext, vnext);
+#pragma unroll 1
+    for (int f = 0; f < nfill; ++f) {
+      const int st = f & 1;
+      const uint4 zc = znext;
+      const bool valid = vnext;
+      load_z(f + 1, znext, vnext);                   // the next fill's rows are requested now
+      const uint32_t row = row0 + (uint32_t)st * phi_bytes;
+      // the stage is free once the dC MMAs of its previous fill are done
+      if (f > 1) mbar_wait(pempty + pg * 2 + st, (uint32_t)((f >> 1) - 1) & 1u, wc);
+#pragma unroll 1
+      for (int i = 0; i < 2; ++i) {                  // 4 keys per pass (small body, see the dz role)
+        const uint32_t zw[2] = {i ? zc.z : zc.x, i ? zc.w : zc.y};
+        const uint32_t old = st ? (i ? sav[1][1] : sav[1][0]) : (i ? sav[0][1] : sav[0][0]);
+        uint32_t now = 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (f > 1) {
+            const uint32_t c0 = (old >> (8 * q)) & 0xffu, c1 = c0 + 1u;
+            sts32(row + (c0 + (c0 >> 2) * 252u) * 4u, 0u);
+            sts32(row + (c1 + (c1 >> 2) * 252u) * 4u, 0u);
+          }
+          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+          uint32_t x0, x1, s0;
+          phi_pair_s(zz, P.g, (uint32_t)(kh * 8 + i * 4 + q) * halfL, x0, x1, s0);
+          if (!valid) { x0 = 0u; x1 = 0u; }
+          const uint32_t s1 = s0 + 1u;
+          sts32(row + (s0 + (s0 >> 2) * 252u) * 4u, x0);
+          sts32(row + (s1 + (s1 >> 2) * 252u) * 4u, x1);
+          now |= s0 << (8 * q);
+        }
+        if (st) { if (i) sav[1][1] = now; else sav[1][0] = now; }
+        else { if (i) sav[0][1] = now; else sav[0][0] = now; }
+      }
+      fence_async_smem();
+      mbar_arrive(pfull + pg * 2 + st);
+    }
+  } else {
+    reg_dec<kRegsAux>();
+    if (warp == 16) {
+      // ---------------------------------------------------------------- S MMAs (both groups)
+      if (lane == 0) {
+        mbar_wait(tfull, 0, wc);
+        const uint32_t rb = (uint32_t)(r / 8) * 128u;
+        const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
+        const uint32_t idesc = instr_desc(0, 0, 0, 0, 128, (int)bcols);
+        // whichever group is ready first is served (the groups drift apart; serving them in a fixed
+        // order would tie each to the slower one)
+        int it[2] = {0, 0};
+        const int total[2] = {4 * ((ntiles + 1) / 2), 4 * (ntiles / 2)};
+        long long t_last = clock64();
+        while ((it[0] < total[0] || it[1] < total[1]) && !*abort_flag) {
+          bool progressed = false;
+#pragma unroll
+          for (int pg = 0; pg < 2; ++pg) {
+            if (it[pg] >= total[pg]) continue;
+            const int k = it[pg], ti = pg + 2 * (k >> 2), qt = k & 3, sb = k & 1, b = ti % kGRing;
+            if (qt == 0 && !mbar_test_wait(gfull + b, (uint32_t)(ti / kGRing) & 1u)) continue;
+            if (k > 1 && !mbar_test_wait(sempty + pg * 2 + sb, (uint32_t)((k >> 1) - 1) & 1u)) continue;
+            tc_fence_after();
+            uint32_t a_lo = desc_lo(smem_u32(g_base + (size_t)b * g_bytes), 2048u);
+            uint32_t b_lo = desc_lo(smem_u32(t_base) + (uint32_t)qt * (uint32_t)(LP / 2) * rb, 128u);
+            const uint32_t d_addr = tmem_base + (uint32_t)(pg * 2 + sb) * bcols;
+            for (int ks = 0; ks < r / 16; ++ks) {
+              umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, ks > 0 ? 1u : 0u);
+              a_lo += 4096u >> 4;
+              b_lo += 256u >> 4;
+            }
+            umma_commit(sfull + pg * 2 + sb);
+            if (qt == 3) umma_commit(gempty + b);        // this issuer is done with the g tile
+            ++it[pg];
+            progressed = true;
+          }
+          if (progressed) t_last = clock64();
+          else if (clock64() - t_last > P.wait_cycles) wait_give_up(wc);
+          else __nanosleep(kPollNs);
+        }
+        umma_commit(done + 0);
+      }
+    } else if (warp == 17) {
+      // ---------------------------------------------------------------- dC MMAs (both groups)
+      if (lane == 0) {
+        const uint32_t idesc = instr_desc(0, 0, 1, 1, 128, r);
+        const uint32_t a_hi = desc_hi(1024u), b_hi = desc_hi(2048u);
+        int it[2] = {0, 0};
+        const int total[2] = {2 * ((ntiles + 1) / 2), 2 * (ntiles / 2)};
+        bool first = true;
+        long long t_last = clock64();
+        while ((it[0] < total[0] || it[1] < total[1]) && !*abort_flag) {
+          bool progressed = false;
+#pragma unroll
+          for (int pg = 0; pg < 2; ++pg) {
+            if (it[pg] >= total[pg]) continue;
+            const int f = it[pg], ti = pg + 2 * (f >> 1), st = f & 1, b = ti % kGRing;
+            if (!mbar_test_wait(pfull + pg * 2 + st, (uint32_t)(f >> 1) & 1u)) continue;
+            if (!mbar_test_wait(gfull + b, (uint32_t)(ti / kGRing) & 1u)) continue;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(phi_base + (size_t)(pg * 2 + st) * phi_bytes);
+            // tokens 64 * st .. of the g tile: token groups 8 * st ..
+            const uint32_t b_lo0 = desc_lo(smem_u32(g_base + (size_t)b * g_bytes) + (uint32_t)st * 8u * 128u, 128u);
+            for (int mt = 0; mt < P.mtiles; ++mt) {
+              uint32_t a_lo = desc_lo(a_addr + (uint32_t)mt * 16u * 1024u, 128u);
+              uint32_t b_lo = b_lo0;
+              const uint32_t d_addr = tmem_base + dcol0 + (uint32_t)(mt * r);
+              umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, first ? 0u : 1u);
+#pragma unroll
+              for (int ks = 1; ks < 4; ++ks) {
+                a_lo += 256u >> 4;
+                b_lo += 256u >> 4;
+                umma_f16_split(d_addr, a_lo, a_hi, b_lo, b_hi, idesc, 1u);
+              }
+            }
+            first = false;
+            umma_commit(pempty + pg * 2 + st);
+            if (st == 1) umma_commit(gempty + b);
+            ++it[pg];
+            progressed = true;
+          }
+          if (progressed) t_last = clock64();
+          else if (clock64() - t_last > P.wait_cycles) wait_give_up(wc);
+          else __nanosleep(kPollNs);
+        }
+        umma_commit(done + 1);
+      }
+    } else if (warp == 18) {
+      // ---------------------------------------------------------------- loader
+      if (lane == 0) {
+        mbar_arrive_expect_tx(tfull, 2 * t_bytes);
+        bulk_g2s(t_base, reinterpret_cast<const uint8_t*>(P.timg) + (size_t)(key0 / kChunkKeys) * t_bytes,
+                 2 * t_bytes, tfull);
+        for (int ti = 0; ti < ntiles; ++ti) {
+          const int b = ti % kGRing;
+          if (ti >= kGRing) mbar_wait(gempty + b, (uint32_t)((ti / kGRing) - 1) & 1u, wc);
+          if (*abort_flag) break;
+          mbar_arrive_expect_tx(gfull + b, g_bytes);
+          bulk_g2s(g_base + (size_t)b * g_bytes,
+                   reinterpret_cast<const uint8_t*>(P.gimg) + (size_t)(tile_begin + ti) * g_bytes, g_bytes, gfull + b);
+        }
+        if (*abort_flag) {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000) {}
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 16) {
+    mbar_wait_drain(done + 0, 0, P.wait_cycles);
+    mbar_wait_drain(done + 1, 0, P.wait_cycles);
+    tc_fence_after();
+    tmem_free(tmem_base, tmem_cols);
   }
 }
 
@@ -665,6 +1081,40 @@ bool plan_dc(const skv_problem& p, DcPlan* o) {
   return false;
 }
 
+struct FusedPlan { int lb, mtiles, slabs, splits; int64_t tiles_total, tiles_per_split; size_t smem; };
+
+// The fused kernel covers shapes whose slab fits: even L up to 24 (16 keys x L rows in three M-tiles),
+// r small enough for the tensor-memory plan, h a multiple of the slab.
+bool plan_fused(const skv_problem& p, FusedPlan* o) {
+  if (p.L % 2 || p.L > 24 || p.h % kSlabKeys || p.N < 1) return false;
+  const int lb = (p.L - 1 + 7) / 8;
+  if (lb < 1 || lb > 3) return false;
+  const int mtiles = (kSlabKeys * p.L + 127) / 128;
+  if (2 * kChunkKeys * 8 * lb + mtiles * p.r > 512) return false;
+  const size_t phi_bytes = (size_t)((kSlabKeys * p.L + 7) / 8) * 1024;      // one 64-token stage
+  const size_t smem = 4 * phi_bytes + (size_t)kGRing * 128 * p.r * 2 + 2 * (size_t)kChunkKeys * 8 * lb * p.r * 2 + 256;
+  if (smem > kSmemMax) return false;
+  // the last M-tile of the last stage reads past the stage: that read must stay inside the allocation
+  if (3 * phi_bytes + (size_t)mtiles * 16 * 1024 > smem) return false;
+  o->lb = lb;
+  o->mtiles = mtiles;
+  o->slabs = p.h / kSlabKeys;
+  o->smem = smem;
+  o->tiles_total = (p.N + 127) / 128;
+  const int64_t tt = o->tiles_total;
+  int best = 1;
+  double best_eff = 0.0;
+  const int64_t max_splits = tt / 4 < 1 ? 1 : (tt / 4 > 32 ? 32 : tt / 4);
+  for (int ns = 1; ns <= max_splits; ++ns) {
+    const double waves = (double)o->slabs * ns / kPlanSMs;
+    const double eff = waves / (double)(int64_t)(waves + 0.999999);
+    if (eff > best_eff + 0.04) { best_eff = eff; best = ns; }
+  }
+  o->tiles_per_split = (tt + best - 1) / best;
+  o->splits = (int)((tt + o->tiles_per_split - 1) / o->tiles_per_split);
+  return true;
+}
+
 size_t timg_bytes(const skv_problem& p) {
   const int lb = (p.L - 1 + 7) / 8;
   return align256((size_t)p.h * 8 * lb * p.r * sizeof(__half));
@@ -687,7 +1137,10 @@ bool bwd_eligible(const skv_problem& p) {
 size_t bwd_scratch_bytes(const skv_problem& p) {
   DcPlan d;
   if (!plan_dc(p, &d)) return 0;
-  return 256 + gimg_bytes(p) + timg_bytes(p) + align256((size_t)d.splits * p.h * p.L * p.r * sizeof(float));
+  int splits = d.splits;
+  FusedPlan f;
+  if (plan_fused(p, &f) && f.splits > splits) splits = f.splits;     // whichever path a call takes fits
+  return 256 + gimg_bytes(p) + timg_bytes(p) + align256((size_t)splits * p.h * p.L * p.r * sizeof(float));
 }
 
 int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const void* g_act, int64_t gas,
@@ -717,6 +1170,62 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     if (cudaGetLastError() != cudaSuccess) return SKV_ERR_LAUNCH;
   }
 
+  FusedPlan fp;
+  if (fused_backward_enabled() && dz && (dC || dC_cast) && plan_fused(p, &fp)) {
+    const size_t pieces = (size_t)p.h * 8 * fp.lb * (p.r / 8);
+    const unsigned tgrid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
+    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, 8 * fp.lb, p.r);
+    note_launches(1);
+    BfParams P;
+    P.z = (const __nv_bfloat16*)z;
+    P.zs = zs;
+    P.g_act = (const __nv_bfloat16*)g_act;
+    P.gas = gas;
+    P.dz = (__nv_bfloat16*)dz;
+    P.dzs = dzs;
+    P.gimg = gimg;
+    P.timg = timg;
+    P.amax_bits = amax;
+    P.part = part;
+    P.N = p.N;
+    P.h = p.h;
+    P.L = p.L;
+    P.r = p.r;
+    P.g = c.g;
+    P.act = p.activation;
+    P.coef = p.lambda_scale * c.g.scale;
+    P.mtiles = fp.mtiles;
+    P.tiles_per_split = fp.tiles_per_split;
+    P.tiles_total = fp.tiles_total;
+    P.status = c.status;
+    P.wait_cycles = wait_cycle_limit();
+    dim3 grid((unsigned)fp.slabs, (unsigned)fp.splits);
+    cudaError_t err = cudaErrorInvalidValue;
+#define SKV_BF_CASE(LB_, NC_, COND_)                                                                               \
+  if (err == cudaErrorInvalidValue && fp.lb == LB_ && (COND_)) {                                                   \
+    if (p.activation == SKV_ACT_RELU_SQ) {                                                                         \
+      err = cudaFuncSetAttribute(tc_bwd_fused_kernel<LB_, NC_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)fp.smem);                                                                    \
+      if (err == cudaSuccess) tc_bwd_fused_kernel<LB_, NC_, true><<<grid, kBfThreads, fp.smem, c.stream>>>(P);            \
+    } else {                                                                                                       \
+      err = cudaFuncSetAttribute(tc_bwd_fused_kernel<LB_, NC_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,\
+                                 (int)fp.smem);                                                                    \
+      if (err == cudaSuccess) tc_bwd_fused_kernel<LB_, NC_, false><<<grid, kBfThreads, fp.smem, c.stream>>>(P);           \
+    }                                                                                                              \
+  }
+    SKV_BF_CASE(3, 21, p.L == 22) SKV_BF_CASE(2, 15, p.L == 16)
+    SKV_BF_CASE(1, 8, true) SKV_BF_CASE(2, 16, true) SKV_BF_CASE(3, 24, true)
+#undef SKV_BF_CASE
+    note_launches(1);
+    if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }
+    const size_t elems = (size_t)p.h * p.L * p.r;
+    const unsigned rgrid = (unsigned)((elems + 255) / 256 < 4096 ? (elems + 255) / 256 : 4096);
+    tc_dc_reduce_kernel<<<rgrid, 256, 0, c.stream>>>(part, fp.splits, elems, p.lambda_scale, amax, dC,
+                                                     (__nv_bfloat16*)dC_cast);
+    note_launches(1);
+    return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_LAUNCH;
+  }
+
   if (dz) {
     const size_t pieces = (size_t)p.h * 8 * zp.lb * (p.r / 8);
     const unsigned tgrid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
@@ -742,6 +1251,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.chunks_total = p.h / kChunkKeys;
     P.chunks_per_split = zp.chunks_per_split;
     P.tstages = zp.tstages;
+    P.wait_cycles = wait_cycle_limit();
     P.status = c.status;
     const int64_t tiles = (p.N + 128 * zp.groups - 1) / (128 * zp.groups);
     dim3 grid((unsigned)tiles, (unsigned)zp.splits);
@@ -785,6 +1295,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.tiles_per_split = dp.tiles_per_split;
     P.tiles_total = dp.tiles_total;
     P.status = c.status;
+    P.wait_cycles = wait_cycle_limit();
     dim3 grid((unsigned)dp.slabs, (unsigned)dp.splits);
     cudaError_t err;
     if (dp.kch == 16) {

@@ -12,9 +12,17 @@ namespace tc {
 constexpr int32_t kStatusTimeoutFwd = 0x1;
 constexpr int32_t kStatusTimeoutDz = 0x2;
 constexpr int32_t kStatusTimeoutDc = 0x4;
+constexpr int32_t kStatusTimeoutBwd = 0x8;
 
-// A wait gives up after this many clock cycles (about two seconds at 2 GHz).
-constexpr long long kWaitCycles = 4000000000LL;
+// A wait gives up after this many clock cycles unless the host set another limit (about two
+// seconds at 2 GHz).  The limit travels in the kernel parameters so that a test can make a wait
+// run out within a millisecond.
+constexpr long long kDefaultWaitCycles = 4000000000LL;
+
+// Test hooks, set through skv_debug_set (host side, read at launch time).
+long long wait_cycle_limit();        // current limit of every bounded wait
+int debug_skip_copy();               // 1: the forward's loader leaves out its first code-table copy
+bool fused_backward_enabled();       // 1: dz and dC run as one kernel where its plan fits (default: two kernels)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -43,24 +51,73 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep up to `ns` nanoseconds and is woken when
+// the phase completes, so a waiting warp does not compete for issue slots with the working ones.
+#ifndef SKV_WAIT_HINT_NS
+#define SKV_WAIT_HINT_NS 2000
+#endif
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)SKV_WAIT_HINT_NS)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking test of a phase (try_wait may suspend the thread for a while; a thread that polls
+// several barriers in turn uses this form).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 
-// Bounded wait.  `abort` is a CTA-wide flag in shared memory: once any wait of the CTA has run
-// out, every later wait returns at once, so the kernel always drains (with invalid results and
-// `code` recorded in the status word) instead of hanging.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int32_t* status,
-                                          int32_t code) {
+// What a bounded wait needs: `abort` is a CTA-wide flag in shared memory (once any wait of the
+// CTA has run out, every later wait returns at once, so the kernel always drains, with invalid
+// results and `code` recorded in the caller's status word, instead of hanging).
+struct WaitCtx {
+  volatile int* abort;
+  int32_t* status;
+  int32_t code;
+  long long limit;
+};
+
+__device__ __forceinline__ void wait_give_up(const WaitCtx& w) {
+  *w.abort = 1;
+  if (w.status) atomicOr(w.status, w.code);
+}
+
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   if (mbar_try_wait(bar, parity)) return;
   const long long t0 = clock64();
   int spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63) == 0) {
-      if (*abort) return;
-      if (clock64() - t0 > kWaitCycles) {
-        *abort = 1;
-        if (status) atomicOr(status, code);
+  while (!mbar_try_wait_sleep(bar, parity)) {
+    if ((++spins & 15) == 0) {
+      if (*w.abort) return;
+      if (clock64() - t0 > w.limit) {
+        wait_give_up(w);
         return;
       }
     }
+  }
+}
+
+// Wait that ignores the abort flag: used once at the end of a kernel for the barrier that the last
+// tcgen05.commit arrives on, so that tensor memory is not freed (and the CTA does not exit) while
+// MMAs issued before a time-out are still running.  They finish by themselves, so this returns.
+__device__ __forceinline__ void mbar_wait_drain(uint64_t* bar, uint32_t parity, long long limit) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > limit) return;
   }
 }
 
@@ -201,8 +258,10 @@ __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 
 // key's segment starts (key-in-chunk * L / 2).
 // The weights use B1 = 1 - B0 - B2 (partition of unity), masked by 0 <= u <= G.
 // ---------------------------------------------------------------------------------------------
+// `kw` is the word distance between consecutive 16-byte chunks of a row minus 4: 508 for tiles of
+// 128 token rows (2048 bytes per chunk column), 252 for tiles of 64.
 __device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t wq, uint32_t& x0, uint32_t& x1,
-                                         uint32_t& wo0, uint32_t& wo1) {
+                                         uint32_t& wo0, uint32_t& wo1, uint32_t kw = 508u) {
   const Knot k = knot_of(zz, g);
   const float t = k.tau, omt = 1.0f - t;
   const float hm = k.in_range ? 0.5f : 0.0f;
@@ -214,8 +273,24 @@ __device__ __forceinline__ void phi_pair(float zz, const GridParams& g, uint32_t
   x0 = p01 << sh;
   x1 = __funnelshift_l(p01, p2, sh);
   const uint32_t s0 = wq + ((uint32_t)k.bin >> 1), s1 = s0 + 1u;
-  wo0 = s0 + (s0 >> 2) * 508u;
-  wo1 = s1 + (s1 >> 2) * 508u;
+  wo0 = s0 + (s0 >> 2) * kw;
+  wo1 = s1 + (s1 >> 2) * kw;
+}
+
+// phi_pair with the word index s0 of the first word (the second is s0 + 1) instead of offsets.
+__device__ __forceinline__ void phi_pair_s(float zz, const GridParams& g, uint32_t wq, uint32_t& x0, uint32_t& x1,
+                                           uint32_t& s0) {
+  const Knot k = knot_of(zz, g);
+  const float t = k.tau, omt = 1.0f - t;
+  const float hm = k.in_range ? 0.5f : 0.0f;
+  const float B0 = (hm * omt) * omt;
+  const float B2 = (hm * t) * t;
+  const float B1 = fmaf(2.0f, hm, -B0) - B2;
+  const uint32_t p01 = pack_h2(B0, B1), p2 = pack_h2(B2, 0.0f);
+  const uint32_t sh = (k.tbits & 1u) << 4;
+  x0 = p01 << sh;
+  x1 = __funnelshift_l(p01, p2, sh);
+  s0 = wq + ((uint32_t)k.bin >> 1);
 }
 
 // Knot-dependent part of phi_pair only: the two f16x2 words and the index (bin >> 1) of the first

@@ -49,6 +49,8 @@ struct FwdParams {
   int32_t* status;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   int cstages;              // depth of the code-table ring (2..4)
+  long long wait_cycles;     // limit of every bounded wait, in clock cycles
+  int skip_copy;             // test hook: the loader leaves out the copy of its first chunk
 };
 
 template <int GROUPS>
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
   uint64_t* done = cempty + kMaxCStages;          // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wc{abort_flag, P.status, kStatusTimeoutFwd, P.wait_cycles};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk_begin = blockIdx.y * P.chunks_per_split;
@@ -119,8 +122,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
       if (ci + 1 < nch && valid) znext = __ldg(reinterpret_cast<const uint4*>(zrow + (ci + 1) * kChunkKeys));
       const uint32_t row = smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes) + t_off;
       if (ci >= kStages) {
-        mbar_wait(empty + s * GROUPS + grp, (uint32_t)((ci / kStages) - 1) & 1u, abort_flag, P.status,
-                  kStatusTimeoutFwd);
+        mbar_wait(empty + s * GROUPS + grp, (uint32_t)((ci / kStages) - 1) & 1u, wc);
         if (valid) {
 #pragma unroll
           for (int q = 0; q < kChunkKeys; ++q) {
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
     }
 
     // epilogue: accumulator -> float32 partial of this key split
-    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    mbar_wait(done, 0, wc);
     tc_fence_after();
     float* prow = P.partial + ((size_t)blockIdx.y * P.N + (valid ? n : 0)) * r;
     const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(grp * r);
@@ -181,10 +183,11 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
         const int s = ci % kStages;
         const uint32_t par = (uint32_t)(ci / kStages) & 1u;
         const int cs = ci % CS;
-        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, wc);
         const uint32_t b_lo0 = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
         for (int grp = 0; grp < GROUPS; ++grp) {
-          mbar_wait(full + s * GROUPS + grp, par, abort_flag, P.status, kStatusTimeoutFwd);
+          mbar_wait(full + s * GROUPS + grp, par, wc);
+          if (*abort_flag) break;                    // draining: issue nothing more
           tc_fence_after();
           uint32_t a_lo = desc_lo(smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes), P.a_lbo);
           uint32_t b_lo = b_lo0;
@@ -197,6 +200,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
           }
           umma_commit(empty + s * GROUPS + grp);
         }
+        if (*abort_flag) break;
         umma_commit(cempty + cs);
       }
       umma_commit(done);
@@ -208,8 +212,9 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % CS;
         if (ci >= CS)
-          mbar_wait(cempty + s, (uint32_t)((ci / CS) - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+          mbar_wait(cempty + s, (uint32_t)((ci / CS) - 1) & 1u, wc);
         if (*abort_flag) break;
+        if (ci == 0 && P.skip_copy) continue;      // test hook: nothing ever completes cfull[0]
         mbar_arrive_expect_tx(cfull + s, c_bytes);
         bulk_g2s(c_base + (size_t)s * c_bytes, src + (size_t)ci * c_bytes, c_bytes, cfull + s);
       }
@@ -224,7 +229,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
   __syncthreads();
   if (warp == 4 * GROUPS) {
     // the accumulator has been read (or the CTA is draining): make sure no MMA is still running
-    mbar_wait(done, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    mbar_wait_drain(done, 0, P.wait_cycles);
     tc_fence_after();
     tmem_free(tmem_base, tmem_cols);
   }
@@ -280,6 +285,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   uint64_t* done = cempty + kMaxTaCStages;        // [group]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + GROUPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wc{abort_flag, P.status, kStatusTimeoutFwd, P.wait_cycles};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk_begin = blockIdx.y * P.chunks_per_split;
@@ -337,7 +343,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         if (ci > 0) {
-          mbar_wait(empty + grp * 2 + half, (uint32_t)(ci - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+          mbar_wait(empty + grp * 2 + half, (uint32_t)(ci - 1) & 1u, wc);
           tc_fence_after();
         }
         // The first NSTH keys of the half go through the staging row: their stores and loads are
@@ -394,7 +400,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       if (arow && valid) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
     }
     // epilogue: accumulator -> float32 partial of this key split
-    mbar_wait(done + grp, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    mbar_wait(done + grp, 0, wc);
     tc_fence_after();
     float* prow = P.partial + ((size_t)blockIdx.y * P.N + (valid ? n : 0)) * r;
     const uint32_t daddr = lane_addr + (uint32_t)(kChunkKeys * HLP);
@@ -420,12 +426,13 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       const uint32_t d_addr = a_addr0 + (uint32_t)(kChunkKeys * HLP);
       for (int ci = 0; ci < nch; ++ci) {
         const int cs = ci % CS;
-        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, wc);
         uint32_t b_lo = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
         uint32_t a_addr = a_addr0;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          mbar_wait(full + grp * 2 + half, (uint32_t)ci & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+          mbar_wait(full + grp * 2 + half, (uint32_t)ci & 1u, wc);
+          if (*abort_flag) break;                    // draining: issue nothing more
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < kHalfSteps; ++ks) {     // 8 columns of A (16 K elements) per step
@@ -435,6 +442,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           }
           umma_commit(empty + grp * 2 + half);
         }
+        if (*abort_flag) break;
         umma_commit(cempty + cs);
       }
       umma_commit(done + grp);
@@ -446,8 +454,9 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % CS;
         if (ci >= CS)
-          mbar_wait(cempty + s, (uint32_t)((ci / CS) - 1) & 1u, abort_flag, P.status, kStatusTimeoutFwd);
+          mbar_wait(cempty + s, (uint32_t)((ci / CS) - 1) & 1u, wc);
         if (*abort_flag) break;
+        if (ci == 0 && P.skip_copy) continue;      // test hook: nothing ever completes cfull[0]
         mbar_arrive_expect_tx(cfull + s, c_bytes);
         bulk_g2s(c_base + (size_t)s * c_bytes, src + (size_t)ci * c_bytes, c_bytes, cfull + s);
       }
@@ -459,7 +468,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   }
   __syncthreads();
   if (warp == 5 * GROUPS) {
-    for (int i = 0; i < GROUPS; ++i) mbar_wait(done + i, 0, abort_flag, P.status, kStatusTimeoutFwd);
+    for (int i = 0; i < GROUPS; ++i) mbar_wait_drain(done + i, 0, P.wait_cycles);
     tc_fence_after();
     tmem_free(tmem_base, tmem_cols);
   }
@@ -628,6 +637,8 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.chunks_per_split = f.chunks_per_split;
   P.status = c.status;
   P.cstages = f.cstages;
+  P.wait_cycles = wait_cycle_limit();
+  P.skip_copy = debug_skip_copy();
   // A: Phi tile, K-major; core matrices of 8 tokens x 8 k: 128 B apart along tokens, 2048 B along k
   P.a_lbo = 2048;
   P.a_sbo = 128;

@@ -138,7 +138,9 @@ def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scal
 
 def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0,
                      with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True):
-    """Gradients for ``grad_out`` of :func:`feature_forward`.
+    """Gradients for ``grad_out`` of :func:`feature_forward`: one ``[N, h+r]`` (or ``[N, r]``) tensor,
+    consumed in place through a base pointer and a row stride per half, or a ``(g_act, g_delta)``
+    pair of separate tensors.
 
     Returns ``(dz or None, dC_f32 or None, dC_cast or None)``; ``dC_cast`` (dtype of ``C``) is only
     produced for bf16 problems when ``cast_dC`` is set.
@@ -150,10 +152,25 @@ def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", 
     z = _rows(z)
     C = C.contiguous()
     N, h, r, L = p.N, p.h, p.r, p.L
-    width = h + r if with_base else r
-    if tuple(grad_out.shape) != (N, width):
-        raise ValueError(f"grad_out must be [N, {width}], got {tuple(grad_out.shape)}")
-    go = _rows(grad_out.to(z.dtype) if grad_out.dtype != z.dtype else grad_out)
+    def _as_rows(t, cols, what):
+        if tuple(t.shape) != (N, cols):
+            raise ValueError(f"{what} must be [N, {cols}], got {tuple(t.shape)}")
+        return _rows(t.to(z.dtype) if t.dtype != z.dtype else t)
+
+    if isinstance(grad_out, (tuple, list)):
+        # the two halves as separate tensors (each with its own row stride): nothing is concatenated
+        if not with_base or len(grad_out) != 2:
+            raise ValueError("a (g_act, g_delta) pair needs with_base=True and exactly two tensors")
+        ga = _as_rows(grad_out[0], h, "g_act")
+        gd = _as_rows(grad_out[1], r, "g_delta")
+        gact_ptr, gact_stride = _ptr(ga), ga.stride(0)
+        gdelta_ptr, gdelta_stride = _ptr(gd), gd.stride(0)
+    else:
+        go = _as_rows(grad_out, h + r if with_base else r, "grad_out")
+        esz = go.element_size()
+        gact_ptr = ctypes.c_void_p(go.data_ptr()) if with_base else None
+        gdelta_ptr = ctypes.c_void_p(go.data_ptr() + (h * esz if with_base else 0))
+        gact_stride = gdelta_stride = go.stride(0)
     with torch.cuda.device(z.device):
         dz = torch.empty((N, h), dtype=z.dtype, device=z.device) if need_dz else None
         dC = torch.empty((h, L, r), dtype=torch.float32, device=z.device) if need_dC else None
@@ -161,11 +178,8 @@ def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", 
         if need_dC and cast_dC and z.dtype != torch.float32:
             dC_cast = torch.empty((h, L, r), dtype=z.dtype, device=z.device)
         scratch, nbytes = _scratch(lib, p, _lib.SKV_OP_BACKWARD, z.device)
-        esz = go.element_size()
-        gact_ptr = ctypes.c_void_p(go.data_ptr()) if with_base else None
-        gdelta_ptr = ctypes.c_void_p(go.data_ptr() + (h * esz if with_base else 0))
         code = lib.skv_feature_backward(
-            ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), gact_ptr, go.stride(0), gdelta_ptr, go.stride(0),
+            ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), gact_ptr, gact_stride, gdelta_ptr, gdelta_stride,
             _ptr(dz), h, _ptr(dC), _ptr(dC_cast), _ptr(scratch), nbytes, _ptr(status_word(z.device)),
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(code)

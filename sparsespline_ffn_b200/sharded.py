@@ -100,8 +100,9 @@ class KeyShardedSplineFeature(torch.autograd.Function):
         z, C = ctx.saved_tensors
         lo, hi, G, act, lam = ctx.cfg
         need_dz, need_dC = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        go = torch.cat([g_act.to(z.dtype), g_delta.to(z.dtype)], dim=1)
-        dz, dC32 = _local_backward(z.detach(), C.detach(), go, lo, hi, G, act, lam, True, need_dz, need_dC)
+        # the two halves go to the library with their own pointers and strides (no [N, h+r] copy)
+        dz, dC32 = _local_backward(z.detach(), C.detach(), (g_act, g_delta), lo, hi, G, act, lam, True, need_dz,
+                                   need_dC)
         dC = dC32.to(C.dtype) if need_dC else None
         return dz, dC, None, None, None, None, None, None
 

@@ -25,9 +25,12 @@ def _oracle_forward(z, C, lo, hi, G_, act, lam, with_base, delta_f32):
 
 def _oracle_backward(z, C, go, lo, hi, G_, act, lam, with_base, need_dz, need_dC):
     h = z.shape[1]
-    g = go.float().numpy()
-    dz, dC = oc.feature_backward(z.float().numpy(), C.float().numpy(), g[:, h:] if with_base else g,
-                                 g[:, :h] if with_base else None, lo, hi, G_, act, lam)
+    if isinstance(go, (tuple, list)):                 # the key-sharded mode passes (g_act, g_delta)
+        g_a, g_d = go[0].float().numpy(), go[1].float().numpy()
+    else:
+        g = go.float().numpy()
+        g_a, g_d = (g[:, :h], g[:, h:]) if with_base else (None, g)
+    dz, dC = oc.feature_backward(z.float().numpy(), C.float().numpy(), g_d, g_a, lo, hi, G_, act, lam)
     return (torch.from_numpy(dz).to(z.dtype) if need_dz else None,
             torch.from_numpy(dC.astype(np.float32)) if need_dC else None)
 
