@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define SKV_ABI_VERSION 1
+#define SKV_ABI_VERSION 2
 
 enum skv_error {
   SKV_OK = 0,
@@ -41,7 +41,9 @@ enum skv_error {
 enum skv_dtype { SKV_BF16 = 0, SKV_F32 = 1 };
 enum skv_activation { SKV_ACT_RELU_SQ = 0, SKV_ACT_IDENTITY = 1, SKV_ACT_GELU = 2 };
 /* SKV_IMPL_AUTO picks the tcgen05 kernels when the shape is eligible (bf16, r a multiple of 16
- * up to 128, even L, h a multiple of 8, 16-byte aligned rows) and the CUDA-core kernels otherwise. */
+ * up to 128, L up to 64, h a multiple of 8, 16-byte aligned rows) and the CUDA-core kernels
+ * otherwise.  The CUDA-core kernels are the float32 tier and a correctness fallback, tens of
+ * times slower at production sizes: skv_resolve_impl tells which family a problem gets. */
 enum skv_impl { SKV_IMPL_AUTO = 0, SKV_IMPL_SIMT = 1, SKV_IMPL_TCGEN05 = 2 };
 enum skv_op { SKV_OP_FORWARD = 0, SKV_OP_BACKWARD = 1 };
 
@@ -61,6 +63,9 @@ typedef struct skv_problem {
   int32_t impl;        /* enum skv_impl */
   int32_t delta_f32;   /* forward only: 1 = write lambda*delta as float32 whatever dtype is (the
                           key-sharded mode sums partial residuals across GPUs in float32) */
+  int32_t dz_f32;      /* backward only, tcgen05 kernels: 1 = write dz as float32 (before its rounding
+                          to the dtype of z), so that a systematic error of dz can be measured; the
+                          dz pointer and stride are then in float32 elements */
 } skv_problem;
 
 /* ABI version of the loaded library (SKV_ABI_VERSION). */
@@ -130,8 +135,9 @@ int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_
  * synchronisation.  This call itself uses no cudaMalloc, cudaFree or allocating library
  * routine.  (Nothing is stated here about recording it into a CUDA graph.)
  *  - A problem whose skv_scratch_bytes(p, SKV_OP_FORWARD) exceeds the array is refused with
- *    SKV_ERR_NOALLOC_LIMIT (at h = 5120, L = 22, r = 32, N = 8192 tokens fit and N = 16384
- *    do not; use skv_feature_forward with caller-owned scratch beyond the limit).
+ *    SKV_ERR_NOALLOC_LIMIT (at h = 5120, L = 22, r = 32, N = 4096 tokens fit and N = 8192
+ *    do not; the need is not monotonic in N because the number of key splits depends on it,
+ *    so ask skv_scratch_bytes; use skv_feature_forward with caller-owned scratch beyond the limit).
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress, with that device current); make that first call before any stream
  *    capture begins.

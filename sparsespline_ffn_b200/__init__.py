@@ -13,4 +13,7 @@ from .kernels.flash_spline_feature_autograd import (  # noqa: F401
     flash_spline_feature,
 )
 
-__all__ = ["FlashSplineFeature", "flash_spline_feature", "FlashSplineDelta", "flash_spline_delta"]
+from .rl_spline_kv import RLSplineKV, RLSplineKVConfig  # noqa: F401,E402
+
+__all__ = ["FlashSplineFeature", "flash_spline_feature", "FlashSplineDelta", "flash_spline_delta",
+           "RLSplineKV", "RLSplineKVConfig"]

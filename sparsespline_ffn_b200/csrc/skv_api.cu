@@ -18,7 +18,7 @@ static std::atomic<int> g_fused_bwd{0};
 namespace tc {
 long long wait_cycle_limit() { return g_wait_cycles.load(std::memory_order_relaxed); }
 int debug_skip_copy() { return g_skip_copy.load(std::memory_order_relaxed); }
-bool fused_backward_enabled() { return g_fused_bwd.load(std::memory_order_relaxed) != 0; }
+int fused_backward_roles() { return g_fused_bwd.load(std::memory_order_relaxed); }
 }  // namespace tc
 }  // namespace skv
 
@@ -123,7 +123,7 @@ int skv_debug_set(int what, int64_t value) {
       skv::g_skip_copy.store(value != 0, std::memory_order_relaxed);
       return SKV_OK;
     case SKV_DEBUG_FUSED_BACKWARD:
-      skv::g_fused_bwd.store(value != 0, std::memory_order_relaxed);
+      skv::g_fused_bwd.store(value == 1 ? 3 : (value == 2 ? 1 : (value == 3 ? 2 : 0)), std::memory_order_relaxed);
       return SKV_OK;
     default:
       return SKV_ERR_UNSUPPORTED;
@@ -190,11 +190,13 @@ int skv_feature_backward(const skv_problem* p, const void* z, int64_t z_stride, 
     return SKV_ERR_SHAPE;
   const int impl = resolve(*p);
   if (impl < 0) return impl;
+  const bool dz32 = p->dz_f32 && p->dtype == SKV_BF16;          // float32 dz of a bf16 problem: tcgen05 kernels only
+  if (dz32 && impl != SKV_IMPL_TCGEN05) return SKV_ERR_UNSUPPORTED;
   if (impl == SKV_IMPL_TCGEN05) {
     if (!aligned(z, 16) || !aligned(C, 16) || !aligned(g_delta, 16) || (g_act && !aligned(g_act, 16)) ||
         (dz && !aligned(dz, 16)) || z_stride % 8 || gdelta_stride % 8 || (g_act && gact_stride % 8) ||
-        (dz && dz_stride % 8)) {
-      if (p->impl == SKV_IMPL_TCGEN05) return SKV_ERR_ALIGN;
+        (dz && dz_stride % (dz32 ? 4 : 8))) {
+      if (p->impl == SKV_IMPL_TCGEN05 || dz32) return SKV_ERR_ALIGN;
     } else {
       if (!scratch || scratch_bytes < tc_scratch_bytes(*p, SKV_OP_BACKWARD)) return SKV_ERR_SCRATCH;
       return tc_backward(c, z, z_stride, C, g_act, gact_stride, g_delta, gdelta_stride, dz, dz_stride, dC_f32,

@@ -39,34 +39,12 @@ constexpr size_t kSmemMax = 227 * 1024;
 
 size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
-// Power-of-two scale from the bit pattern of max|g|: max|g| * scale lies in [2^12, 2^13).
-__device__ __forceinline__ void g_scales(uint32_t amax_bits, float& scale, float& inv) {
-  const int e = (int)((amax_bits >> 23) & 0xff);
-  if (e == 0 || e == 255) { scale = 1.0f; inv = 1.0f; return; }
-  int se = 127 + 12 - (e - 127);           // biased exponent of 2^(12 - (e-127))
-  se = se < 1 ? 1 : (se > 254 ? 254 : se);
-  scale = __uint_as_float((uint32_t)se << 23);
-  inv = __uint_as_float((uint32_t)(254 - se) << 23);
-}
-
-__global__ void tc_amax_kernel(const __nv_bfloat16* __restrict__ g, int64_t gds, int64_t N, int r,
-                               uint32_t* __restrict__ amax_bits) {
-  const int64_t total = N * r;
-  uint32_t m = 0;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const float v = fabsf(__bfloat162float(g[(i / r) * gds + (i % r)]));
-    if (v == v) m = max(m, __float_as_uint(v));
-  }
-  for (int s = 16; s >= 1; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
-  if ((threadIdx.x & 31) == 0 && m) atomicMax(amax_bits, m);
-}
-
 // g [N][r] bf16 -> scaled f16 image, per 128-token tile the 8x8 core matrices (token rows of 16
 // bytes) at ((cg * 16 + tg) * 128) bytes; rows past N are zero.
 __global__ void tc_pack_g_kernel(const __nv_bfloat16* __restrict__ g, int64_t gds, int64_t N, int r, int64_t tiles,
                                  const uint32_t* __restrict__ amax_bits, __half* __restrict__ img) {
   float scale, inv;
-  g_scales(*amax_bits, scale, inv);
+  pow2_scales(*amax_bits, scale, inv);
   const int cgs = r / 8;
   const int64_t pieces = tiles * 128 * cgs;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (int64_t)gridDim.x * blockDim.x) {
@@ -91,7 +69,9 @@ __global__ void tc_pack_g_kernel(const __nv_bfloat16* __restrict__ g, int64_t gd
 // L-1.. are zero: per 8-key chunk the [8*LP x r] tile as 8x8 core matrices, core (rowg, cg) at
 // ((rowg * r/8 + cg) * 128) bytes.
 __global__ void tc_pack_t_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int LP,
-                                 int r) {
+                                 int r, const uint32_t* __restrict__ amax_bits) {
+  float cscale, cinv;
+  pow2_scales(amax_bits[kAmaxC], cscale, cinv);
   const int rows_per_chunk = kChunkKeys * LP;
   const int cgs = r / 8;
   const size_t pieces = (size_t)h * LP * cgs;
@@ -108,6 +88,7 @@ __global__ void tc_pack_t_kernel(const __nv_bfloat16* __restrict__ C, __half* __
       else
         v[q] = __bfloat162float(base[(size_t)(m - 1) * r + q]) - 2.0f * __bfloat162float(base[(size_t)m * r + q]) +
                __bfloat162float(base[(size_t)(m + 1) * r + q]);
+      v[q] *= cscale;                                   // a power of two: exact
     }
     const int chunk = (int)(rowg / rows_per_chunk);
     const int k = (int)(rowg % rows_per_chunk);
@@ -137,6 +118,7 @@ struct DzParams {
   float coef;                // lambda * scale
   int chunks_total, chunks_per_split;
   int tstages;               // depth of the transformed-table ring (2..kTStages)
+  int dz_f32;                // dz is float32 [N][dzs] instead of bf16
   int32_t* status;
   long long wait_cycles;     // limit of every bounded wait, in clock cycles
 };
@@ -257,8 +239,10 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
     const __nv_bfloat16* garow = P.g_act ? P.g_act + nn * P.gas + (int64_t)chunk_begin * kChunkKeys : nullptr;
     __nv_bfloat16* dzrow = P.dz + nn * P.dzs + (int64_t)chunk_begin * kChunkKeys;
     float gscale, ginv;
-    g_scales(*P.amax_bits, gscale, ginv);
-    const float coef = P.coef * ginv;
+    pow2_scales(*P.amax_bits, gscale, ginv);
+    float cscale, cinv;
+    pow2_scales(P.amax_bits[kAmaxC], cscale, cinv);
+    const float coef = P.coef * ginv * cinv;
     const int act = P.act;
     const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)grp * ncols;
     uint4 znext = valid && nch > 0 ? __ldg(reinterpret_cast<const uint4*>(zrow)) : make_uint4(0, 0, 0, 0);
@@ -301,10 +285,17 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       }
       tc_fence_before();
       mbar_arrive(sempty + grp);
-      if (valid)
-        *reinterpret_cast<uint4*>(dzrow + ci * kChunkKeys) =
-            make_uint4(pack_bf2(outv[0], outv[1]), pack_bf2(outv[2], outv[3]), pack_bf2(outv[4], outv[5]),
-                       pack_bf2(outv[6], outv[7]));
+      if (valid) {
+        if (P.dz_f32) {
+          float* o = reinterpret_cast<float*>(P.dz) + nn * P.dzs + (int64_t)(chunk_begin + ci) * kChunkKeys;
+          *reinterpret_cast<float4*>(o) = make_float4(outv[0], outv[1], outv[2], outv[3]);
+          *reinterpret_cast<float4*>(o + 4) = make_float4(outv[4], outv[5], outv[6], outv[7]);
+        } else {
+          *reinterpret_cast<uint4*>(dzrow + ci * kChunkKeys) =
+              make_uint4(pack_bf2(outv[0], outv[1]), pack_bf2(outv[2], outv[3]), pack_bf2(outv[4], outv[5]),
+                         pack_bf2(outv[6], outv[7]));
+        }
+      }
     }
   } else if (warp == 4 * GROUPS) {
     // ------------------------------------------------------------------ MMA issue
@@ -312,6 +303,8 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       mbar_wait(gfull, 0, wc);
       const uint32_t rb = (uint32_t)(r / 8) * 128u;          // bytes between 8-row groups of the T image
       const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
+      // The groups are served in a fixed order.  (Serving whichever group has released its S columns
+      // first, by polling both, was measured slower: 1.32 ms against 1.21 ms at the d20 shape.)
       for (int ci = 0; ci < nch; ++ci) {
         const int s = ci % TS;
         mbar_wait(tfull + s, (uint32_t)(ci / TS) & 1u, wc);
@@ -383,6 +376,7 @@ struct DcParams {
   int64_t N;
   int h, L, r;
   GridParams g;
+  int LR;                    // knot rows per key in the Phi^T tile: L rounded up to even (pad row zero)
   int kch;                   // keys per chunk (8 or 16)
   int mtiles;                // 128-row MMA tiles per chunk
   int slab_chunks;           // chunks per CTA slab
@@ -396,7 +390,7 @@ struct DcParams {
 template <int KCH>
 __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int L = P.L, r = P.r;
+  const int L = P.L, LR = P.LR, r = P.r;
   const uint32_t phi_bytes = (uint32_t)P.mtiles * 16u * 2048u;     // [m groups][16 token groups][8 tok][8 m]
   const uint32_t g_bytes = (uint32_t)(128 * r * 2);
   uint8_t* phi_base = smem;                                         // [2][phi_bytes]
@@ -412,7 +406,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
   const WaitCtx wc{abort_flag, P.status, kStatusTimeoutDc, P.wait_cycles};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rows = KCH * L;                                          // knot rows per chunk
+  const int rows = KCH * LR;                                         // (padded) knot rows per chunk
   const int key0 = blockIdx.x * P.slab_chunks * KCH;
   const int nchunks = min(P.slab_chunks, (P.h - key0 + KCH - 1) / KCH);
   const int64_t tile_begin = (int64_t)blockIdx.y * P.tiles_per_split;
@@ -449,7 +443,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
     const int t = tid & 127;
     const uint32_t t_off = (uint32_t)(t & 7) * 16u + (uint32_t)(t >> 3) * 128u;
     const uint32_t row = smem_u32(phi_base + (size_t)pg * phi_bytes) + t_off;
-    const uint32_t halfL = (uint32_t)L >> 1;
+    const uint32_t halfL = (uint32_t)LR >> 1;
     uint32_t saved[KCH];
 #pragma unroll
     for (int i = 0; i < KCH; ++i) saved[i] = 0;
@@ -510,10 +504,11 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
     float* part = P.part + (size_t)blockIdx.y * P.h * L * r;
     for (int ch = pg; ch < nchunks; ch += 2) {
       for (int mt = 0; mt < P.mtiles; ++mt) {
-        const int rr = mt * 128 + lane_row;                        // knot row within the chunk
-        const int key = key0 + ch * KCH + rr / L;
-        const bool ok = rr < rows && key < P.h;
-        float* dst = part + ((size_t)(key0 + ch * KCH) * L + rr) * r;
+        const int rr = mt * 128 + lane_row;                        // padded knot row within the chunk
+        const int kl = rr / LR, bb = rr - kl * LR;
+        const int key = key0 + ch * KCH + kl;
+        const bool ok = rr < rows && key < P.h && bb < L;           // the pad row of an odd L is dropped
+        float* dst = part + ((size_t)key * L + bb) * r;
         const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((ch * P.mtiles + mt) * r);
         for (int c0 = 0; c0 < r; c0 += 16) {
           float v[16];
@@ -600,7 +595,7 @@ __global__ void tc_dc_reduce_kernel(const float* __restrict__ part, int splits, 
                                     const uint32_t* __restrict__ amax_bits, float* __restrict__ dC,
                                     __nv_bfloat16* __restrict__ dC_cast) {
   float gscale, ginv;
-  g_scales(*amax_bits, gscale, ginv);
+  pow2_scales(*amax_bits, gscale, ginv);
   const float f = lambda * ginv;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (size_t)gridDim.x * blockDim.x) {
     float s = 0.0f;
@@ -656,6 +651,8 @@ struct BfParams {
   int act;
   float coef;                // lambda * scale
   int mtiles;                // 128-row MMA tiles over the slab's 16*L knot rows
+  int dz_f32;                // dz is float32 [N][dzs] instead of bf16
+  int roles;                 // bit 0: the dz role runs, bit 1: the Phi role and the dC MMAs run
   int64_t tiles_per_split, tiles_total;
   int32_t* status;
   long long wait_cycles;
@@ -664,6 +661,7 @@ struct BfParams {
 constexpr int kSlabKeys = 16;
 constexpr int kGRing = 3;
 constexpr int kBfThreads = 640;
+constexpr int kAux0 = 16;                      // first helper warp
 // register counts per role (multiples of 8); 256 * kRegsDz + 256 * kRegsPhi + 128 * kRegsAux must
 // not exceed kBfThreads * the count the kernel is compiled for (96)
 constexpr int kRegsDz = 128, kRegsPhi = 88, kRegsAux = 40;
@@ -713,7 +711,8 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
   while (tmem_cols < dcol0 + (uint32_t)(P.mtiles * r)) tmem_cols <<= 1;
 
   if (tid == 0) {
-    for (int i = 0; i < kGRing; ++i) { mbar_init(gfull + i, 1); mbar_init(gempty + i, 2); }
+    const uint32_t issuers = (uint32_t)((P.roles & 1) + ((P.roles >> 1) & 1));
+    for (int i = 0; i < kGRing; ++i) { mbar_init(gfull + i, 1); mbar_init(gempty + i, issuers); }
     mbar_init(tfull, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(sfull + i, 1);
@@ -731,7 +730,7 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     const uint32_t n16 = 4 * phi_bytes / 16;
     for (uint32_t i = tid; i < n16; i += blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
   }
-  if (warp == 16) tmem_alloc(tmem_slot, tmem_cols);
+  if (warp == kAux0) tmem_alloc(tmem_slot, tmem_cols);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -745,8 +744,10 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     const int t = tid & 127;
     const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)pg * 2u * bcols;
     float gscale, ginv;
-    g_scales(*P.amax_bits, gscale, ginv);
-    const float coef = P.coef * ginv;
+    pow2_scales(*P.amax_bits, gscale, ginv);
+    float cscale, cinv;
+    pow2_scales(P.amax_bits[kAmaxC], cscale, cinv);
+    const float coef = P.coef * ginv * cinv;
     const int act = P.act;
     const bool has_ga = P.g_act != nullptr;
     auto load_rows = [&](int ti, uint4 (&zv)[2], uint4 (&gv)[2], bool& valid, __nv_bfloat16*& dzrow) {
@@ -767,62 +768,68 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     __nv_bfloat16* dznext;
     load_rows(pg, znext, ganext, vnext, dznext);
     int use = 0;                                     // S blocks this group has consumed
-    uint32_t keep0 = 0u, keep1 = 0u;                 // outputs of the even block until the odd one is done
-    for (int ti = pg; ti < ntiles; ti += 2) {
+    for (int ti = pg; ti < ntiles && (P.roles & 1); ti += 2) {
       const uint4 zq[2] = {znext[0], znext[1]}, gaq[2] = {ganext[0], ganext[1]};
       const bool valid = vnext;
       __nv_bfloat16* dzrow = dznext;
       load_rows(ti + 2, znext, ganext, vnext, dznext);   // the group's next tile: request its rows now
 #pragma unroll 1
-      for (int bk = 0; bk < 4; ++bk, ++use) {            // four S blocks of 4 keys; small body on purpose:
-        // this loop shares the instruction cache of its SM sub-partition with the Phi role's loop
-        const uint4 zc = (bk & 2) ? zq[1] : zq[0], gc = (bk & 2) ? gaq[1] : gaq[0];
-        const uint32_t zw[2] = {(bk & 1) ? zc.z : zc.x, (bk & 1) ? zc.w : zc.y};
-        const uint32_t gw[2] = {(bk & 1) ? gc.z : gc.x, (bk & 1) ? gc.w : gc.y};
-        const uint32_t blk = trow + (uint32_t)(use & 1) * bcols;
-        uint32_t bufa[LB][8], bufb[LB][8];
-        float outv[4];
-        mbar_wait(sfull + pg * 2 + (use & 1), (uint32_t)(use >> 1) & 1u, wc);
-        tc_fence_after();
-        tmem_ld_key<LB>(blk, bufa);
+      for (int hf = 0; hf < 2; ++hf) {               // 8 keys per pass: two S blocks of 4 keys, unrolled
+        const uint4 zc = hf ? zq[1] : zq[0], gc = hf ? gaq[1] : gaq[0];
+        const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
+        const uint32_t gw[4] = {gc.x, gc.y, gc.z, gc.w};
+        float outv[kChunkKeys];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (q & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
-          if (q + 1 < 4) {
-            if (q & 1) tmem_ld_key<LB>(blk + (uint32_t)((q + 1) * LP), bufa);
-            else tmem_ld_key<LB>(blk + (uint32_t)((q + 1) * LP), bufb);
+        for (int qt = 0; qt < 2; ++qt, ++use) {
+          const uint32_t blk = trow + (uint32_t)(use & 1) * bcols;
+          uint32_t bufa[LB][8], bufb[LB][8];
+          mbar_wait(sfull + pg * 2 + (use & 1), (uint32_t)(use >> 1) & 1u, wc);
+          tc_fence_after();
+          tmem_ld_key<LB>(blk, bufa);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int q = qt * 4 + q4;
+            if (q4 & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
+            if (q4 + 1 < 4) {
+              if (q4 & 1) tmem_ld_key<LB>(blk + (uint32_t)((q4 + 1) * LP), bufa);
+              else tmem_ld_key<LB>(blk + (uint32_t)((q4 + 1) * LP), bufb);
+            }
+            const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
+            const float u = __fmaf_rn(__fsub_rn(zz, P.g.lo), P.g.scale, 0.0f);
+            const bool active = __float_as_uint(u) <= __float_as_uint(P.g.Gm1f);
+            const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
+            const float acc = (q4 & 1) ? dz_key_sum<LB, NC>(bufb, uc) : dz_key_sum<LB, NC>(bufa, uc);
+            float o = active ? coef * acc : 0.0f;
+            if (has_ga) {
+              const float ga = (q & 1) ? bf_hi(gw[q >> 1]) : bf_lo(gw[q >> 1]);
+              const float dphi = RELU ? 2.0f * fmaxf(zz, 0.0f) : act_grad(zz, act);
+              o = fmaf(ga, dphi, o);
+            }
+            outv[q] = o;
           }
-          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
-          const float u = __fmaf_rn(__fsub_rn(zz, P.g.lo), P.g.scale, 0.0f);
-          const bool active = __float_as_uint(u) <= __float_as_uint(P.g.Gm1f);
-          const float uc = fminf(fmaxf(u, 0.0f), P.g.Gm1f);
-          const float acc = (q & 1) ? dz_key_sum<LB, NC>(bufb, uc) : dz_key_sum<LB, NC>(bufa, uc);
-          float o = active ? coef * acc : 0.0f;
-          if (has_ga) {
-            const float ga = (q & 1) ? bf_hi(gw[q >> 1]) : bf_lo(gw[q >> 1]);
-            const float dphi = RELU ? 2.0f * fmaxf(zz, 0.0f) : act_grad(zz, act);
-            o = fmaf(ga, dphi, o);
-          }
-          outv[q] = o;
+          tc_fence_before();
+          mbar_arrive(sempty + pg * 2 + (use & 1));
         }
-        tc_fence_before();
-        mbar_arrive(sempty + pg * 2 + (use & 1));
-        const uint32_t o01 = pack_bf2(outv[0], outv[1]), o23 = pack_bf2(outv[2], outv[3]);
-        if (bk & 1) {
-          if (valid) *reinterpret_cast<uint4*>(dzrow + (bk - 1) * 4) = make_uint4(keep0, keep1, o01, o23);
-        } else {
-          keep0 = o01;
-          keep1 = o23;
+        if (valid) {
+          if (P.dz_f32) {
+            float* o = reinterpret_cast<float*>(P.dz) + (dzrow - P.dz) + hf * 8;
+            *reinterpret_cast<float4*>(o) = make_float4(outv[0], outv[1], outv[2], outv[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(outv[4], outv[5], outv[6], outv[7]);
+          } else {
+            *reinterpret_cast<uint4*>(dzrow + hf * 8) =
+                make_uint4(pack_bf2(outv[0], outv[1]), pack_bf2(outv[2], outv[3]), pack_bf2(outv[4], outv[5]),
+                           pack_bf2(outv[6], outv[7]));
+          }
         }
       }
     }
     // ---- epilogue: the slab's accumulators -> float32 partial of this token split
-    mbar_wait(done + 1, 0, wc);
+    if (P.roles & 2) mbar_wait(done + 1, 0, wc);
     tc_fence_after();
     const int lane_row = (warp & 3) * 32 + lane;
     const int rows = kSlabKeys * L;
     float* part = P.part + ((size_t)blockIdx.y * P.h + key0) * L * r;
-    for (int mt = pg; mt < P.mtiles; mt += 2) {
+    for (int mt = pg; mt < P.mtiles && (P.roles & 2); mt += 2) {
       const int rr = mt * 128 + lane_row;
       const bool ok = rr < rows;
       float* dst = part + (size_t)rr * r;
@@ -838,7 +845,7 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
       }
     }
     tc_fence_before();
-  } else if (warp < 16) {
+  } else if (warp < kAux0) {
     // ------------------------------------------------------------------ Phi role
     reg_dec<kRegsPhi>();
     const int pg = (warp - 8) >> 2;
@@ -862,7 +869,7 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     bool vnext;
     load_z(0, znext, vnext);
 #pragma unroll 1
-    for (int f = 0; f < nfill; ++f) {
+    for (int f = 0; f < nfill && (P.roles & 2); ++f) {
       const int st = f & 1;
       const uint4 zc = znext;
       const bool valid = vnext;
@@ -899,9 +906,9 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     }
   } else {
     reg_dec<kRegsAux>();
-    if (warp == 16) {
+    if (warp == kAux0) {
       // ---------------------------------------------------------------- S MMAs (both groups)
-      if (lane == 0) {
+      if (lane == 0 && (P.roles & 1)) {
         mbar_wait(tfull, 0, wc);
         const uint32_t rb = (uint32_t)(r / 8) * 128u;
         const uint32_t a_hi = desc_hi(128u), b_hi = desc_hi(rb);
@@ -939,9 +946,9 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
         }
         umma_commit(done + 0);
       }
-    } else if (warp == 17) {
+    } else if (warp == kAux0 + 1) {
       // ---------------------------------------------------------------- dC MMAs (both groups)
-      if (lane == 0) {
+      if (lane == 0 && (P.roles & 2)) {
         const uint32_t idesc = instr_desc(0, 0, 1, 1, 128, r);
         const uint32_t a_hi = desc_hi(1024u), b_hi = desc_hi(2048u);
         int it[2] = {0, 0};
@@ -984,7 +991,7 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
         }
         umma_commit(done + 1);
       }
-    } else if (warp == 18) {
+    } else if (warp == kAux0 + 2) {
       // ---------------------------------------------------------------- loader
       if (lane == 0) {
         mbar_arrive_expect_tx(tfull, 2 * t_bytes);
@@ -1006,9 +1013,9 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     }
   }
   __syncthreads();
-  if (warp == 16) {
-    mbar_wait_drain(done + 0, 0, P.wait_cycles);
-    mbar_wait_drain(done + 1, 0, P.wait_cycles);
+  if (warp == kAux0) {
+    if (P.roles & 1) mbar_wait_drain(done + 0, 0, P.wait_cycles);
+    if (P.roles & 2) mbar_wait_drain(done + 1, 0, P.wait_cycles);
     tc_fence_after();
     tmem_free(tmem_base, tmem_cols);
   }
@@ -1048,8 +1055,9 @@ bool plan_dz(const skv_problem& p, DzPlan* o) {
 struct DcPlan { int kch, mtiles, slab_chunks, slabs, splits; int64_t tiles_total, tiles_per_split; size_t smem; };
 
 bool plan_dc(const skv_problem& p, DcPlan* o) {
+  const int LR = (p.L + 1) & ~1;
   for (int kch = 16; kch >= 8; kch /= 2) {
-    const int rows = kch * p.L;
+    const int rows = kch * LR;
     const int mtiles = (rows + 127) / 128;
     if (mtiles > 3) continue;
     const size_t smem = 2 * (size_t)mtiles * 16 * 2048 + 2 * (size_t)128 * p.r * 2 + 256;
@@ -1161,7 +1169,13 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
   {
     const int64_t total = p.N * p.r;
     const unsigned grid = (unsigned)((total + 1023) / 1024 < 1184 ? (total + 1023) / 1024 : 1184);
-    tc_amax_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)g_delta, gds, p.N, p.r, amax);
+    tc_amax_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)g_delta, gds, p.N, p.r, amax + kAmaxG);
+    if (dz) {
+      const int64_t crows = (int64_t)p.h * p.L;
+      const unsigned cgrid = (unsigned)((crows * p.r + 1023) / 1024 < 1184 ? (crows * p.r + 1023) / 1024 : 1184);
+      tc_amax_kernel<<<cgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, p.r, crows, p.r, amax + kAmaxC);
+      note_launches(1);
+    }
     const int64_t tiles = ((p.N + 255) / 256) * 2;
     const int64_t pieces = tiles * 128 * (p.r / 8);
     const unsigned pgrid = (unsigned)((pieces + 255) / 256 < 2368 ? (pieces + 255) / 256 : 2368);
@@ -1171,10 +1185,10 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
   }
 
   FusedPlan fp;
-  if (fused_backward_enabled() && dz && (dC || dC_cast) && plan_fused(p, &fp)) {
+  if (fused_backward_roles() && dz && (dC || dC_cast) && plan_fused(p, &fp)) {
     const size_t pieces = (size_t)p.h * 8 * fp.lb * (p.r / 8);
     const unsigned tgrid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
-    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, 8 * fp.lb, p.r);
+    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, 8 * fp.lb, p.r, amax);
     note_launches(1);
     BfParams P;
     P.z = (const __nv_bfloat16*)z;
@@ -1195,6 +1209,8 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.act = p.activation;
     P.coef = p.lambda_scale * c.g.scale;
     P.mtiles = fp.mtiles;
+    P.dz_f32 = p.dz_f32;
+    P.roles = fused_backward_roles();
     P.tiles_per_split = fp.tiles_per_split;
     P.tiles_total = fp.tiles_total;
     P.status = c.status;
@@ -1229,7 +1245,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
   if (dz) {
     const size_t pieces = (size_t)p.h * 8 * zp.lb * (p.r / 8);
     const unsigned tgrid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
-    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, 8 * zp.lb, p.r);
+    tc_pack_t_kernel<<<tgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, timg, p.h, p.L, 8 * zp.lb, p.r, amax);
     note_launches(1);
     DzParams P;
     P.z = (const __nv_bfloat16*)z;
@@ -1251,6 +1267,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.chunks_total = p.h / kChunkKeys;
     P.chunks_per_split = zp.chunks_per_split;
     P.tstages = zp.tstages;
+    P.dz_f32 = p.dz_f32;
     P.wait_cycles = wait_cycle_limit();
     P.status = c.status;
     const int64_t tiles = (p.N + 128 * zp.groups - 1) / (128 * zp.groups);
@@ -1289,6 +1306,7 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     P.L = p.L;
     P.r = p.r;
     P.g = c.g;
+    P.LR = (p.L + 1) & ~1;
     P.kch = dp.kch;
     P.mtiles = dp.mtiles;
     P.slab_chunks = dp.slab_chunks;

@@ -22,7 +22,8 @@ constexpr long long kDefaultWaitCycles = 4000000000LL;
 // Test hooks, set through skv_debug_set (host side, read at launch time).
 long long wait_cycle_limit();        // current limit of every bounded wait
 int debug_skip_copy();               // 1: the forward's loader leaves out its first code-table copy
-bool fused_backward_enabled();       // 1: dz and dC run as one kernel where its plan fits (default: two kernels)
+int fused_backward_roles();          // 0: two kernels (default); 3: dz and dC as one kernel where its plan fits
+                                     // (1 / 2: that kernel with only its dz / only its dC role, for timing)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -226,6 +227,58 @@ __host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int a_mn
   return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)a_mn_major << 15) |
          ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+
+// Range scaling of the f16 operand images.  f16 has a 5-bit exponent: values below 6e-5 lose
+// precision and below 3e-8 vanish, which a freshly initialised (near-zero) code table or a small
+// upstream gradient would hit.  Each image is therefore multiplied by a power of two chosen from
+// the largest magnitude of its source (max * scale lies in [2^12, 2^13); the transformed table's
+// second differences then stay below 2^15), and the float32 results are multiplied by the exact
+// inverse.
+__device__ __forceinline__ void pow2_scales(uint32_t amax_bits, float& scale, float& inv) {
+  const int e = (int)((amax_bits >> 23) & 0xff);
+  if (e == 0 || e == 255) { scale = 1.0f; inv = 1.0f; return; }
+  int se = 127 + 12 - (e - 127);           // biased exponent of 2^(12 - (e-127))
+  se = se < 1 ? 1 : (se > 254 ? 254 : se);
+  scale = __uint_as_float((uint32_t)se << 23);
+  inv = __uint_as_float((uint32_t)(254 - se) << 23);
+}
+// Words of the 256-byte header at the start of a call's scratch: bit patterns of max|g_delta| and max|C|.
+constexpr int kAmaxG = 0, kAmaxC = 8;
+
+namespace {
+// Largest magnitude (as a float32 bit pattern, NaN skipped) of a [rows][cols] bf16 array with row stride.
+__global__ void tc_amax_kernel(const __nv_bfloat16* __restrict__ a, int64_t stride, int64_t rows, int cols,
+                               uint32_t* __restrict__ amax_bits) {
+  const int64_t total = rows * cols;
+  uint32_t m = 0;
+  if (stride == cols && (reinterpret_cast<uintptr_t>(a) & 15) == 0) {
+    // contiguous: 16-byte loads; |x| of a bf16 as a float32 bit pattern is its 15 low bits shifted up
+    const int64_t n8 = total / 8;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(a) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t lo = (w[q] << 16) & 0x7fff0000u, hi = w[q] & 0x7fff0000u;
+        if (lo <= 0x7f800000u) m = max(m, lo);          // NaN patterns lie above infinity: skipped
+        if (hi <= 0x7f800000u) m = max(m, hi);
+      }
+    }
+    for (int64_t i = n8 * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+      const float v = fabsf(__bfloat162float(a[i]));
+      if (v == v) m = max(m, __float_as_uint(v));
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+      const float v = fabsf(__bfloat162float(a[(i / cols) * stride + (i % cols)]));
+      if (v == v) m = max(m, __float_as_uint(v));
+    }
+  }
+  for (int s = 16; s >= 1; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(amax_bits, m);
+}
+}  // namespace
 
 // Two float32 -> packed f16x2 (low half = a) as a 32-bit word.
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {

@@ -1,24 +1,22 @@
 // tcgen05 forward of the spline-KV feature operator (bf16 I/O, r a multiple of 16 up to 128,
-// even L, h a multiple of 8).
+// h a multiple of 8).
 //
 //   delta[n, c] = sum_j sum_b Phi[n, (j,b)] * C[j, b, c]
 //
 // is computed as a dense GEMM on the 5th-generation tensor cores: the expanded basis Phi (three
-// non-zero weights per key, at knot rows bin..bin+2) is built per token in shared memory as f16,
-// the code table is staged by TMA bulk copies from an f16 image in the canonical operand layout,
-// and tcgen05.mma accumulates 128-token x r tiles in tensor memory in float32.
+// non-zero weights per key, at knot rows bin..bin+2) is built per token as f16, the code table is
+// staged by TMA bulk copies from a range-scaled f16 image in the canonical operand layout, and
+// tcgen05.mma accumulates 128-token x r tiles in tensor memory in float32.  A small second kernel
+// sums the key splits, applies lambda and casts.
 //
-// Launch shape: grid = (token tiles of 128*GROUPS tokens, key splits).  A CTA walks its keys in
-// chunks of 8 (K extent 8*L per chunk) through a two-stage ring:
-//   warps 0..4*GROUPS-1  producers, one thread per token: read 8 pre-activations, write the
-//                        ReLU^2 half of the output, compute knot interval and weights in
-//                        registers, store the two non-zero 32-bit words of the Phi row segment;
-//                        after the last chunk they read the accumulator from tensor memory and
-//                        store the float32 partial residual of this key split
-//   warp 4*GROUPS        lane 0 issues the MMAs of each chunk and commits to the ring barriers
-//   warp 4*GROUPS+1      lane 0 issues the bulk copies of the code-table image
-// A small second kernel sums the key splits, applies lambda and casts.
+// Two kernels.  tc_forward_ta_kernel (the one used for the knot counts in common use) keeps Phi
+// in tensor memory: every producer thread builds the complete row segment of a key in registers
+// and writes it into its own tensor-memory lane, and the MMA takes its A operand from there.
+// tc_forward_kernel keeps Phi in shared memory (scattered 32-bit stores, bound by shared-memory
+// bandwidth) and serves the remaining knot counts.  Their launch shapes and warp roles are
+// described at each kernel.
 //
+// A key with an odd number of knot rows is padded by one zero row in the operand images.
 // Every mbarrier wait is bounded (skv_tc_common.cuh); a timed-out wait sets the status word and
 // lets the CTA drain.
 #include "skv_tc_common.cuh"
@@ -43,6 +41,7 @@ struct FwdParams {
   float* partial;           // [splits][N][r]
   int64_t N;
   int h, L, r;
+  int LR;                   // knot rows per key in the shared-memory Phi tile: L rounded up to even
   GridParams g;
   int act;
   int chunks_total, chunks_per_split;
@@ -53,10 +52,19 @@ struct FwdParams {
   int skip_copy;             // test hook: the loader leaves out the copy of its first chunk
 };
 
+// Phi in shared memory.  Launch shape: grid = (token tiles of 128*GROUPS tokens, key splits).  A CTA
+// walks its keys in chunks of 8 (K extent 8*LR per chunk) through a two-stage ring:
+//   warps 0..4*GROUPS-1  producers, one thread per token: read 8 pre-activations, write the
+//                        phi(z) half of the output, compute knot interval and weights in
+//                        registers, store the two non-zero 32-bit words of the Phi row segment;
+//                        after the last chunk they read the accumulator from tensor memory and
+//                        store the float32 partial residual of this key split
+//   warp 4*GROUPS        lane 0 issues the MMAs of each chunk and commits to the ring barriers
+//   warp 4*GROUPS+1      lane 0 issues the bulk copies of the code-table image
 template <int GROUPS>
 __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const FwdParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int L = P.L, r = P.r;
+  const int L = P.LR, r = P.r;                                    // padded rows: the pad row stays zero
   const uint32_t phi_bytes = (uint32_t)L * 2048u;                 // 128 tokens x 8L f16
   const uint32_t c_bytes = (uint32_t)(kChunkKeys * L * r * 2);
   uint8_t* phi_base = smem;                                        // [stage][group][phi_bytes]
@@ -477,7 +485,9 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
 // C [h][L][r] bf16 -> f16 image: per 8-key chunk the [8L x r] tile as 8x8 core matrices,
 // core (kg, cg) at ((kg * r/8 + cg) * 128) bytes, row k%8 at 16 bytes, channel c%8 at 2 bytes.
 __global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __restrict__ img, int h, int L, int LP,
-                                 int r) {
+                                 int r, const uint32_t* __restrict__ amax_bits) {
+  float cscale, cinv;
+  pow2_scales(amax_bits[kAmaxC], cscale, cinv);
   const int rows_per_chunk = kChunkKeys * LP;          // LP >= L rows per key in the image, rows L.. are zero
   const int cgs = r / 8;
   const size_t pieces = (size_t)h * LP * cgs;
@@ -492,7 +502,7 @@ __global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) o[q] = pack_h2(bf_lo(w[q]), bf_hi(w[q]));
+    for (int q = 0; q < 4; ++q) o[q] = pack_h2(bf_lo(w[q]) * cscale, bf_hi(w[q]) * cscale);
     __half* dst = img + (size_t)chunk * rows_per_chunk * r + ((size_t)(k >> 3) * cgs + cg) * 64 + (k & 7) * 8;
     *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
   }
@@ -500,7 +510,10 @@ __global__ void tc_pack_c_kernel(const __nv_bfloat16* __restrict__ C, __half* __
 
 template <typename TD>
 __global__ void tc_finalize_kernel(const float* __restrict__ partial, int splits, int64_t N, int r, float lambda,
-                                   TD* __restrict__ out, int64_t ds) {
+                                   const uint32_t* __restrict__ amax_bits, TD* __restrict__ out, int64_t ds) {
+  float cscale, cinv;
+  pow2_scales(amax_bits[kAmaxC], cscale, cinv);
+  lambda *= cinv;                                       // undo the code-table image's range scaling
   const int64_t total = N * r;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     float s = 0.0f;
@@ -517,7 +530,7 @@ struct FwdPlan {
 };
 
 // Half knot-row counts (L/2) the tensor-memory variant is instantiated for.
-bool ta_supported_hl(int hl) { return hl == 8 || hl == 11 || hl == 21; }
+bool ta_supported_hl(int hl) { return hl == 8 || hl == 11 || hl == 12 || hl == 16 || hl == 21; }
 
 size_t fwd_smem(int groups, int cstages, int L, int r) {
   return (size_t)kStages * groups * L * 2048 + (size_t)cstages * kChunkKeys * L * r * 2 + 256;
@@ -525,9 +538,9 @@ size_t fwd_smem(int groups, int cstages, int L, int r) {
 
 bool plan_forward(const skv_problem& p, FwdPlan* out) {
   out->ta = false;
-  const int hl = p.L / 2;
+  const int hl = (p.L + 1) / 2;                       // f16x2 words per key (an odd L leaves one half empty)
   const int hlp = (hl + 1) & ~1;                      // words per key in tensor memory (padded to even)
-  if (p.L % 2 == 0 && ta_supported_hl(hl) && kChunkKeys * hlp + p.r <= 512) {
+  if (ta_supported_hl(hl) && kChunkKeys * hlp + p.r <= 512) {
     int groups = 512 / (kChunkKeys * hlp + p.r);
     if (groups > 4) groups = 4;
     const size_t c_bytes = (size_t)kChunkKeys * 2 * hlp * p.r * 2;
@@ -555,12 +568,13 @@ bool plan_forward(const skv_problem& p, FwdPlan* out) {
       return true;
     }
   }
+  const int LR = (p.L + 1) & ~1;
   int groups = 0;
-  if (fwd_smem(2, 2, p.L, p.r) <= kSmemLimit) groups = 2;
-  else if (fwd_smem(1, 2, p.L, p.r) <= kSmemLimit) groups = 1;
+  if (fwd_smem(2, 2, LR, p.r) <= kSmemLimit) groups = 2;
+  else if (fwd_smem(1, 2, LR, p.r) <= kSmemLimit) groups = 1;
   if (!groups) return false;
   int cstages = 2;
-  while (cstages < kMaxCStages && fwd_smem(groups, cstages + 1, p.L, p.r) <= kSmemLimit) ++cstages;
+  while (cstages < kMaxCStages && fwd_smem(groups, cstages + 1, LR, p.r) <= kSmemLimit) ++cstages;
   out->cstages = cstages;
   const int chunks = p.h / kChunkKeys;
   const int64_t tiles = (p.N + 128 * groups - 1) / (128 * groups);
@@ -576,7 +590,7 @@ bool plan_forward(const skv_problem& p, FwdPlan* out) {
   out->splits = best;
   out->chunks_per_split = (chunks + best - 1) / best;
   out->splits = (chunks + out->chunks_per_split - 1) / out->chunks_per_split;
-  out->smem = fwd_smem(groups, cstages, p.L, p.r);
+  out->smem = fwd_smem(groups, cstages, LR, p.r);
   return true;
 }
 
@@ -587,7 +601,7 @@ size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 bool fwd_eligible(const skv_problem& p) {
   if (p.dtype != SKV_BF16) return false;
   if (p.r % 16 || p.r < 16 || p.r > 128) return false;
-  if (p.L % 2 || p.L < 4 || p.L > 64) return false;
+  if (p.L < 4 || p.L > 64) return false;
   if (p.h % kChunkKeys) return false;
   FwdPlan f;
   return plan_forward(p, &f);
@@ -599,14 +613,19 @@ size_t cimg_bytes(const skv_problem& p) { return align256((size_t)p.h * ((p.L + 
 size_t fwd_scratch_bytes(const skv_problem& p) {
   FwdPlan f;
   if (!plan_forward(p, &f)) return 0;
-  return cimg_bytes(p) + align256((size_t)f.splits * (p.N > 0 ? p.N : 1) * p.r * sizeof(float));
+  return 256 + cimg_bytes(p) + align256((size_t)f.splits * (p.N > 0 ? p.N : 1) * p.r * sizeof(float));
 }
 
-int launch_pack_c(const LaunchCtx& c, const void* C, void* img, int LP) {
+// Largest magnitude of C into the scratch header, then the scaled f16 image.
+int launch_pack_c(const LaunchCtx& c, const void* C, uint32_t* hdr, void* img, int LP) {
+  if (cudaMemsetAsync(hdr, 0, 256, c.stream) != cudaSuccess) return SKV_ERR_LAUNCH;
+  const int64_t crows = (int64_t)c.p.h * c.p.L;
+  const unsigned agrid = (unsigned)((crows * c.p.r + 1023) / 1024 < 1184 ? (crows * c.p.r + 1023) / 1024 : 1184);
+  tc_amax_kernel<<<agrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, c.p.r, crows, c.p.r, hdr + kAmaxC);
   const size_t pieces = (size_t)c.p.h * LP * (c.p.r / 8);
   const unsigned grid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
-  tc_pack_c_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, (__half*)img, c.p.h, c.p.L, LP, c.p.r);
-  note_launches(1);
+  tc_pack_c_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, (__half*)img, c.p.h, c.p.L, LP, c.p.r, hdr);
+  note_launches(2);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_LAUNCH;
 }
 
@@ -616,9 +635,11 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   FwdPlan f;
   if (!plan_forward(p, &f)) return SKV_ERR_UNSUPPORTED;
   if (scratch_bytes < fwd_scratch_bytes(p)) return SKV_ERR_SCRATCH;
-  __half* img = reinterpret_cast<__half*>(scratch);
-  float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + cimg_bytes(p));
-  if (int e = launch_pack_c(c, C, img, f.ta ? ((p.L / 2 + 1) & ~1) * 2 : p.L)) return e;
+  uint32_t* hdr = reinterpret_cast<uint32_t*>(scratch);                 // 256-byte header: max|C|
+  __half* img = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(scratch) + 256);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + 256 + cimg_bytes(p));
+  const int LR = (p.L + 1) & ~1;
+  if (int e = launch_pack_c(c, C, hdr, img, f.ta ? (((p.L + 1) / 2 + 1) & ~1) * 2 : LR)) return e;
 
   FwdParams P;
   P.z = (const __nv_bfloat16*)z;
@@ -631,6 +652,7 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.h = p.h;
   P.L = p.L;
   P.r = p.r;
+  P.LR = LR;
   P.g = c.g;
   P.act = p.activation;
   P.chunks_total = p.h / kChunkKeys;
@@ -651,7 +673,7 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   cudaError_t err = cudaErrorInvalidValue;
   if (f.ta) {
     const unsigned threads = 160 * f.groups + 32;
-    const int hl = p.L / 2;
+    const int hl = (p.L + 1) / 2;
 #define SKV_TA_LAUNCH(G_, HL_, ACT_)                                                                                 \
   {                                                                                                                  \
     err = cudaFuncSetAttribute(tc_forward_ta_kernel<G_, HL_, ACT_, kStagedPerHalf>,                     \
@@ -667,6 +689,8 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   }
     SKV_TA_CASE(1, 8) SKV_TA_CASE(2, 8) SKV_TA_CASE(3, 8) SKV_TA_CASE(4, 8)
     SKV_TA_CASE(1, 11) SKV_TA_CASE(2, 11) SKV_TA_CASE(3, 11) SKV_TA_CASE(4, 11)
+    SKV_TA_CASE(1, 12) SKV_TA_CASE(2, 12) SKV_TA_CASE(3, 12) SKV_TA_CASE(4, 12)
+    SKV_TA_CASE(1, 16) SKV_TA_CASE(2, 16) SKV_TA_CASE(3, 16)
     SKV_TA_CASE(1, 21) SKV_TA_CASE(2, 21)
 #undef SKV_TA_LAUNCH
 #undef SKV_TA_CASE
@@ -683,10 +707,10 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   const int64_t total = p.N * p.r;
   const unsigned fgrid = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
   if (p.delta_f32)
-    tc_finalize_kernel<float><<<fgrid, 256, 0, c.stream>>>(partial, f.splits, p.N, p.r, p.lambda_scale,
+    tc_finalize_kernel<float><<<fgrid, 256, 0, c.stream>>>(partial, f.splits, p.N, p.r, p.lambda_scale, hdr,
                                                            (float*)delta_out, ds);
   else
-    tc_finalize_kernel<__nv_bfloat16><<<fgrid, 256, 0, c.stream>>>(partial, f.splits, p.N, p.r, p.lambda_scale,
+    tc_finalize_kernel<__nv_bfloat16><<<fgrid, 256, 0, c.stream>>>(partial, f.splits, p.N, p.r, p.lambda_scale, hdr,
                                                                    (__nv_bfloat16*)delta_out, ds);
   note_launches(1);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_LAUNCH;

@@ -69,6 +69,39 @@ def _problem(z: torch.Tensor, C: torch.Tensor, grid_lo, grid_hi, G, activation, 
                         dtype=_DTYPES[z.dtype], impl=_lib.SKV_IMPL[impl])
 
 
+_warned_slow: set[tuple] = set()
+
+
+def _warn_if_slow_family(lib, p: _lib.Problem, z: torch.Tensor, aligned_fn) -> None:
+    """One warning per shape when a large bf16 problem is about to run on the CUDA-core kernels
+    (r not a multiple of 16, h not a multiple of 8, a pointer or stride that is not 16-byte
+    aligned, ...): they are a correctness fallback, tens of times slower than the tcgen05 kernels."""
+    if z.dtype != torch.bfloat16 or p.impl != _lib.SKV_IMPL["auto"] or p.N * p.h < (1 << 24):
+        return
+    aligned = bool(aligned_fn())
+    if aligned and lib.skv_resolve_impl(ctypes.byref(p)) == _lib.SKV_IMPL["tcgen05"]:
+        return
+    key = (p.h, p.L, p.r, aligned)
+    if key in _warned_slow:
+        return
+    _warned_slow.add(key)
+    import warnings
+    why = ("a tensor whose base address or row stride is not 16-byte aligned" if not aligned else
+           f"a shape outside the tcgen05 kernels' range (h={p.h}, L={p.L}, r={p.r}: need r % 16 == 0, r <= 128, "
+           "h % 8 == 0, L <= 64)")
+    warnings.warn(f"splinekv_b200: {p.N} x {p.h} bf16 problem runs on the CUDA-core fallback kernels because of "
+                  f"{why}; expect it to be tens of times slower", RuntimeWarning, stacklevel=3)
+
+
+def _aligned16(*tensors) -> bool:
+    for t in tensors:
+        if t is None:
+            continue
+        if t.data_ptr() % 16 or (t.dim() == 2 and (t.stride(0) * t.element_size()) % 16):
+            return False
+    return True
+
+
 def _rows(t: torch.Tensor) -> torch.Tensor:
     """A view or copy of a 2-D tensor with unit inner stride (any row stride is passed through)."""
     if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1]:
@@ -127,6 +160,8 @@ def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scal
             delta_ptr = ctypes.c_void_p(f.data_ptr() + (h * f.element_size() if with_base else 0))
             act_stride = delta_stride = f.stride(0)
             result = f
+        _warn_if_slow_family(lib, p, z, lambda: _aligned16(z, C) and (delta_ptr.value or 0) % 16 == 0
+                             and (delta_stride * (4 if delta_f32 else z.element_size())) % 16 == 0)
         scratch, nbytes = _scratch(lib, p, _lib.SKV_OP_FORWARD, z.device)
         code = lib.skv_feature_forward(
             ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), act_ptr, act_stride, delta_ptr, delta_stride,
@@ -137,13 +172,15 @@ def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scal
 
 
 def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0,
-                     with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True):
+                     with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True, dz_f32=False):
     """Gradients for ``grad_out`` of :func:`feature_forward`: one ``[N, h+r]`` (or ``[N, r]``) tensor,
     consumed in place through a base pointer and a row stride per half, or a ``(g_act, g_delta)``
     pair of separate tensors.
 
     Returns ``(dz or None, dC_f32 or None, dC_cast or None)``; ``dC_cast`` (dtype of ``C``) is only
-    produced for bf16 problems when ``cast_dC`` is set.
+    produced for bf16 problems when ``cast_dC`` is set.  ``dz_f32`` asks the tensor-core kernels of a
+    bf16 problem for ``dz`` before its rounding to bf16 (a float32 tensor), which is how the tests
+    measure a systematic error of ``dz``.
     """
     lib = _lib.load()
     C_in_dtype = C.dtype
@@ -172,11 +209,16 @@ def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", 
         gdelta_ptr = ctypes.c_void_p(go.data_ptr() + (h * esz if with_base else 0))
         gact_stride = gdelta_stride = go.stride(0)
     with torch.cuda.device(z.device):
-        dz = torch.empty((N, h), dtype=z.dtype, device=z.device) if need_dz else None
+        p.dz_f32 = 1 if (dz_f32 and z.dtype != torch.float32) else 0
+        dz = torch.empty((N, h), dtype=torch.float32 if dz_f32 else z.dtype, device=z.device) if need_dz else None
         dC = torch.empty((h, L, r), dtype=torch.float32, device=z.device) if need_dC else None
         dC_cast = None
         if need_dC and cast_dC and z.dtype != torch.float32:
             dC_cast = torch.empty((h, L, r), dtype=z.dtype, device=z.device)
+        _warn_if_slow_family(lib, p, z, lambda: _aligned16(z, C) and (gdelta_ptr.value or 0) % 16 == 0
+                             and (gact_ptr is None or (gact_ptr.value or 0) % 16 == 0)
+                             and (gdelta_stride * z.element_size()) % 16 == 0
+                             and (gact_stride * z.element_size()) % 16 == 0)
         scratch, nbytes = _scratch(lib, p, _lib.SKV_OP_BACKWARD, z.device)
         code = lib.skv_feature_backward(
             ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), gact_ptr, gact_stride, gdelta_ptr, gdelta_stride,

@@ -7,9 +7,11 @@ Run where the reference source tree is available:
 It imports the reference's own PyTorch oracle (``flash_spline_feature_reference``,
 ``_b2_basis_and_bins``, ``flash_spline_delta_backward_ref`` and the CPU path of
 ``FlashSplineFeature`` / ``FlashSplineDelta``), evaluates it in float32 on small
-seeded inputs and stores inputs and outputs in ``spline_kv_golden.npz``.  The
-fixture travels with the repository; the reference does not have to be present
-when the tests run.
+seeded inputs and stores inputs and outputs in ``spline_kv_golden.npz``; a second
+file, ``module_golden.npz``, holds one forward + backward of the reference's
+``RLSplineKVReference`` layer per mode (additive, gelu base, no_base, multiplicative
+gate).  The fixtures travel with the repository; the reference does not have to be
+present when the tests run.
 """
 from __future__ import annotations
 
@@ -67,10 +69,56 @@ def cases():
     return out
 
 
+MODULE_CASES = {
+    # name -> extra config fields of the reference's RLSplineKVConfig
+    "additive": dict(),
+    "additive_gelu": dict(activation="gelu"),
+    "no_base": dict(no_base=True),
+    "multiplicative": dict(gating_mode="multiplicative"),
+}
+
+
+def module_fixture(reference_src):
+    """One forward + backward of the reference's RLSplineKVReference module (CPU, float32, its own
+    PyTorch path) per mode: inputs, parameters, output and every gradient, in module_golden.npz."""
+    sys.path.insert(0, reference_src)
+    from sparsespline_ffn.rl_spline_kv_reference import RLSplineKVConfig, RLSplineKVReference  # noqa: E402
+
+    store = {}
+    for i, (name, extra) in enumerate(MODULE_CASES.items()):
+        torch.manual_seed(100 + i)
+        cfg = RLSplineKVConfig(d=32, h_ratio=2.0, r=16, G=20, grid_lo=-3.0, grid_hi=3.0, lambda_scale=0.5,
+                               c_init_std=0.05, use_kernel=False, **extra)
+        m = RLSplineKVReference(cfg)
+        m.train()                                        # no diagnostics pass
+        with torch.no_grad():
+            m.K.weight.mul_(2.0)                         # spread z over more knot intervals
+            if m.W_d_proj is not None:
+                m.W_d_proj.weight.mul_(30.0)             # a gate that visibly departs from 1
+        x = torch.randn(3, 16, cfg.d).requires_grad_(True)
+        gy = torch.randn(3, 16, cfg.d)
+        y = m(x)
+        y.backward(gy)
+        rec = dict(x=x.detach(), gy=gy, y=y.detach(), dx=x.grad)
+        for pname, prm in m.named_parameters():
+            rec["param." + pname] = prm.detach()
+            rec["grad." + pname] = prm.grad
+        for k, v in rec.items():
+            store[f"{name}/{k}"] = v.numpy()
+    path = os.path.join(HERE, "module_golden.npz")
+    np.savez_compressed(path, **store)
+    print(path, os.path.getsize(path), "bytes;", len(store), "arrays")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference-src", required=True)
+    ap.add_argument("--only", choices=["operator", "module"], help="regenerate one of the two fixture files")
     args = ap.parse_args()
+    if args.only != "operator":
+        module_fixture(args.reference_src)
+    if args.only == "module":
+        return
     sys.path.insert(0, args.reference_src)
     from sparsespline_ffn.rl_spline_kv_reference import (  # noqa: E402
         _b2_basis_and_bins, flash_spline_feature_reference)

@@ -1,0 +1,67 @@
+"""The layer above the operator: this package's RLSplineKV module (K -> feature -> W_out) against
+one forward + backward of the reference's own RLSplineKVReference module, stored in
+tests/golden/module_golden.npz (src/sparsespline_ffn/rl_spline_kv_reference.py:291-364; the
+fixture is written by tests/golden/make_golden.py from the reference's CPU path).  All three
+forward graphs are covered: additive (with the ReLU^2 and the gelu base path), no_base and the
+multiplicative gate; the parameters are loaded through the reference's own state-dict names."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+skv_module = pytest.importorskip("sparsespline_ffn_b200.rl_spline_kv")
+
+CASES = {
+    "additive": dict(),
+    "additive_gelu": dict(activation="gelu"),
+    "no_base": dict(no_base=True),
+    "multiplicative": dict(gating_mode="multiplicative"),
+}
+
+
+@pytest.fixture(scope="module")
+def fixture():
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "module_golden.npz")
+    data = np.load(path)
+    out = {}
+    for key in data.files:
+        case, name = key.split("/", 1)
+        out.setdefault(case, {})[name] = data[key]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_module_matches_the_reference_module(fixture, case, dtype):
+    rec = fixture[case]
+    cfg = skv_module.RLSplineKVConfig(d=32, h_ratio=2.0, r=16, G=20, grid_lo=-3.0, grid_hi=3.0, lambda_scale=0.5,
+                                      c_init_std=0.05, **CASES[case])
+    m = skv_module.RLSplineKV(cfg)
+    state = {k[len("param."):]: torch.from_numpy(v) for k, v in rec.items() if k.startswith("param.")}
+    missing = m.load_state_dict(state, strict=False)
+    assert not missing.unexpected_keys
+    assert set(missing.missing_keys) <= {"grid_lo_buf", "grid_hi_buf"}          # buffers, not parameters
+    # float32 throughout runs the CUDA-core kernels: tight gate.  The bf16 variant keeps float32
+    # weights and GEMMs and runs the operator alone in bf16 (the tensor-core kernels): z is rounded to
+    # bf16 on entry, which moves the result by a few 1e-3 of its largest value
+    m = m.to(device="cuda")
+    m.operator_dtype = None if dtype == torch.float32 else dtype
+    x = torch.from_numpy(rec["x"]).to(device="cuda").requires_grad_(True)
+    y = m(x)
+    y.backward(torch.from_numpy(rec["gy"]).to(device="cuda"))
+    gate = 2e-4 if dtype == torch.float32 else 2e-2
+    if dtype == torch.bfloat16:
+        from sparsespline_ffn_b200 import ops as _ops
+        z = m.K(x.detach().reshape(-1, 32)).to(dtype)
+        assert _ops.resolve_impl(z, m.C.detach().to(dtype), -3.0, 3.0, 20) == "tcgen05"
+    util.assert_parity("y", y, rec["y"], dtype, rel_gate=gate)
+    util.assert_parity("dx", x.grad, rec["dx"], dtype, rel_gate=gate)
+    for name, p in m.named_parameters():
+        util.assert_parity("d" + name, p.grad, rec["grad." + name], dtype, rel_gate=gate)
+    from sparsespline_ffn_b200 import ops
+    ops.check_status(x.device)

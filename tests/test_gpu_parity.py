@@ -29,6 +29,11 @@ SHAPES = [
     (520, 64, 64, 22),
     (260, 64, 16, 22),
     (300, 64, 32, 42),
+    (512, 64, 32, 23),       # odd knot-row counts (one zero pad row in the operand images) and L = 24, 32
+    (300, 40, 16, 31),
+    (200, 24, 32, 9),
+    (512, 64, 32, 24),
+    (512, 64, 32, 32),
 ]
 DTYPES = [torch.float32, torch.bfloat16]
 IMPLS = ["simt", "tcgen05"]
@@ -248,3 +253,73 @@ def test_run_to_run_determinism():
     a = ops.feature_backward(z, C, go, LO, HI, G)
     b = ops.feature_backward(z, C, go, LO, HI, G)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("c_scale", [1e-6, 1e-7, "mixed"], ids=["1e-6", "1e-7", "mixed"])
+def test_small_code_table_magnitudes(c_scale):
+    """A freshly initialised code table is near zero (the reference starts from C = 0,
+    src/sparsespline_ffn/rl_spline_kv_reference.py:44,285): the f16 operand images are range-scaled, so
+    tiny entries keep their precision.  Errors are judged relative to the largest reference value."""
+    N, h, r, G = 1024, 256, 32, 20
+    g = torch.Generator().manual_seed(17)
+    z = (torch.randn(N, h, generator=g) * 1.5).to(torch.bfloat16).cuda()
+    C = torch.randn(h, G + 2, r, generator=g)
+    if c_scale == "mixed":
+        C = C * torch.logspace(-6, -1, h).reshape(h, 1, 1)      # per-key magnitudes from 1e-6 to 0.1
+    else:
+        C = C * c_scale
+    C = C.to(torch.bfloat16).cuda()
+    go = torch.randn(N, h + r, generator=g).to(torch.bfloat16).cuda()
+    _, d32 = ops.feature_forward(z, C, LO, HI, G, "relu_sq", 1.0, delta_f32=True, impl="tcgen05")
+    dz, dC, _ = ops.feature_backward(z, C, go[:, h:], LO, HI, G, "identity", 1.0, with_base=False, impl="tcgen05")
+    _, d_ref = util.oracle_forward(z, C, LO, HI, G, "relu_sq", 1.0)
+    dz_ref, dC_ref = util.oracle_backward(z, C, go[:, h:], LO, HI, G, "identity", 1.0, with_base=False)
+    assert np.abs(d_ref).max() > 0 and np.abs(dz_ref).max() > 0
+    util.assert_parity("delta f32", d32, d_ref, torch.bfloat16, rel_gate=2e-3)
+    util.assert_parity("dz_spline", dz, dz_ref, torch.bfloat16)
+    util.assert_parity("dC", dC, dC_ref, torch.bfloat16)
+    ops.check_status(z.device)
+
+
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] % 16 == 0 and s[2] <= 32 and s[3] <= 24 and s[3] % 2 == 0],
+                         ids=_sid)
+def test_fused_backward_matches_the_two_kernel_backward(shape):
+    """The one-kernel form of the backward (dz and dC roles in one CTA) against the default two
+    kernels and the oracle: dz bit for bit, dC up to the order of the token sum."""
+    from sparsespline_ffn_b200 import _lib
+    N, h, r, L = shape
+    G = L - 2
+    z, C, go = util.make_inputs(N, h, r, G, torch.bfloat16)
+    _impl_or_skip("tcgen05", z, C, G)
+    lib = _lib.load()
+    dz0, dC0, _ = ops.feature_backward(z, C, go, LO, HI, G, "relu_sq", 0.5, impl="tcgen05")
+    lib.skv_debug_set(_lib.SKV_DEBUG_FUSED_BACKWARD, 1)
+    try:
+        launches = int(lib.skv_kernel_launches())
+        dz1, dC1, _ = ops.feature_backward(z, C, go, LO, HI, G, "relu_sq", 0.5, impl="tcgen05")
+        launches = int(lib.skv_kernel_launches()) - launches
+        dz2, dC2, _ = ops.feature_backward(z, C, go[:, h:], LO, HI, G, "identity", 0.5, with_base=False,
+                                           impl="tcgen05")
+    finally:
+        lib.skv_debug_set(_lib.SKV_DEBUG_FUSED_BACKWARD, 0)
+    assert launches == 6, "the fused path launches amax x2, two packs, the fused kernel and the reduce"
+    assert torch.equal(dz0, dz1)
+    scale = dC0.abs().max().item()
+    assert (dC0 - dC1).abs().max().item() <= 1e-5 * scale
+    dz_ref, dC_ref = util.oracle_backward(z, C, go, LO, HI, G, "relu_sq", 0.5)
+    util.assert_parity("dz (fused)", dz1, dz_ref, torch.bfloat16)
+    util.assert_parity("dC (fused)", dC1, dC_ref, torch.bfloat16, bias=True)
+    dz2_ref, dC2_ref = util.oracle_backward(z, C, go[:, h:], LO, HI, G, "identity", 0.5, with_base=False)
+    util.assert_parity("dz_spline (fused)", dz2, dz2_ref, torch.bfloat16)
+    util.assert_parity("dC delta-only (fused)", dC2, dC2_ref, torch.bfloat16, bias=True)
+    ops.check_status(z.device)
+
+
+@pytest.mark.parametrize("L", [9, 15, 21, 22, 23, 24, 31, 32, 33, 41, 42])
+def test_knot_counts_resolve_to_the_tensor_core_kernels(L):
+    """Odd knot-row counts and every count up to the G = 40 grid get the tcgen05 kernels, not the
+    CUDA-core fallback (the reference's fastest forward takes L = 16, 22 and 32 only,
+    src/sparsespline_ffn/cuda_ext/spline_kv_fwd_v11.cu:382-392)."""
+    z = torch.zeros(256, 64, dtype=torch.bfloat16, device="cuda")
+    C = torch.zeros(64, L, 32, dtype=torch.bfloat16, device="cuda")
+    assert ops.resolve_impl(z, C, LO, HI, L - 2) == "tcgen05"

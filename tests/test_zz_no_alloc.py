@@ -58,6 +58,12 @@ def test_noalloc_refuses_problems_beyond_its_array():
     p = _lib.Problem(N=65536, h=5120, L=22, r=32, grid_lo=-5.0, scale=2.0, lambda_scale=1.0,
                      activation=0, dtype=_lib.SKV_BF16, impl=0, delta_f32=0)
     assert lib.skv_scratch_bytes(ctypes.byref(p), 0) > _lib.SKV_NOALLOC_SCRATCH_BYTES
+    # the boundary the header documents for this width: 4096 tokens fit, 8192 do not
+    p.N = 4096
+    assert 0 < lib.skv_scratch_bytes(ctypes.byref(p), 0) <= _lib.SKV_NOALLOC_SCRATCH_BYTES
+    p.N = 8192
+    assert lib.skv_scratch_bytes(ctypes.byref(p), 0) > _lib.SKV_NOALLOC_SCRATCH_BYTES
+    p.N = 65536
     rc = lib.skv_feature_forward_noalloc(ctypes.byref(p), None, 5120, None, None, 0, None, 32, None, None)
     assert rc == -8
     assert b"SKV_NOALLOC_SCRATCH_BYTES" in lib.skv_error_string(rc)
