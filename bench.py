@@ -347,8 +347,8 @@ def main():
     if os.path.exists(tpath):
         with open(tpath) as f:
             rec = json.load(f).get(f"{impl}:{dominant}")
-        if rec:
-            # captured at a reduced token count: the per-token part scales with N, the rest does not
+        if rec and "bytes_per_token" in rec:
+            # captured at two reduced token counts: the per-token part scales with N, the rest does not
             traffic = rec["bytes_per_token"] * N + rec["bytes_fixed"]
     step_tflops = 3 * flops / (ms_per_step * 1e-3) / 1e12
     roofline = dict(bound="tensor", kernel=f"{impl}:{dominant}", achieved=achieved, peak=peaks["bf16_tflops"],
