@@ -97,19 +97,22 @@ __device__ __forceinline__ void wait_give_up(const WaitCtx& w) {
   if (w.status) atomicOr(w.status, w.code);
 }
 
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
-  if (mbar_try_wait(bar, parity)) return;
+// Returns true when the CTA is draining (this wait ran out, or it saw the abort flag while it
+// spun); the fast path, a phase that is already complete, reads nothing but the barrier.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
+  if (mbar_try_wait(bar, parity)) return false;
   const long long t0 = clock64();
   int spins = 0;
   while (!mbar_try_wait_sleep(bar, parity)) {
     if ((++spins & 15) == 0) {
-      if (*w.abort) return;
+      if (*w.abort) return true;
       if (clock64() - t0 > w.limit) {
         wait_give_up(w);
-        return;
+        return true;
       }
     }
   }
+  return false;
 }
 
 // Wait that ignores the abort flag: used once at the end of a kernel for the barrier that the last

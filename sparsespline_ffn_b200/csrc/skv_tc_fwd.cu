@@ -191,11 +191,11 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
         const int s = ci % kStages;
         const uint32_t par = (uint32_t)(ci / kStages) & 1u;
         const int cs = ci % CS;
-        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, wc);
+        bool drain = mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, wc);
         const uint32_t b_lo0 = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
-        for (int grp = 0; grp < GROUPS; ++grp) {
-          mbar_wait(full + s * GROUPS + grp, par, wc);
-          if (*abort_flag) break;                    // draining: issue nothing more
+        for (int grp = 0; grp < GROUPS && !drain; ++grp) {
+          drain = mbar_wait(full + s * GROUPS + grp, par, wc);
+          if (drain) break;                          // draining: issue nothing more
           tc_fence_after();
           uint32_t a_lo = desc_lo(smem_u32(phi_base + (size_t)(s * GROUPS + grp) * phi_bytes), P.a_lbo);
           uint32_t b_lo = b_lo0;
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
           }
           umma_commit(empty + s * GROUPS + grp);
         }
-        if (*abort_flag) break;
+        if (drain) break;
         umma_commit(cempty + cs);
       }
       umma_commit(done);
@@ -434,13 +434,13 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
       const uint32_t d_addr = a_addr0 + (uint32_t)(kChunkKeys * HLP);
       for (int ci = 0; ci < nch; ++ci) {
         const int cs = ci % CS;
-        mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, wc);
+        bool drain = mbar_wait(cfull + cs, (uint32_t)(ci / CS) & 1u, wc);
         uint32_t b_lo = desc_lo(smem_u32(c_base + (size_t)cs * c_bytes), P.b_lbo);
         uint32_t a_addr = a_addr0;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          mbar_wait(full + grp * 2 + half, (uint32_t)ci & 1u, wc);
-          if (*abort_flag) break;                    // draining: issue nothing more
+          drain = drain || mbar_wait(full + grp * 2 + half, (uint32_t)ci & 1u, wc);
+          if (drain) break;                          // draining: issue nothing more
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < kHalfSteps; ++ks) {     // 8 columns of A (16 K elements) per step
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           }
           umma_commit(empty + grp * 2 + half);
         }
-        if (*abort_flag) break;
+        if (drain) break;
         umma_commit(cempty + cs);
       }
       umma_commit(done + grp);
