@@ -569,13 +569,14 @@ def extra_key_sharded(torch, dist, ops, sharded, cfg, rank, world, dev, timed, N
 
 def extra_sweep(torch, ops, cfg, rank, dev, timed, N=131072, steps=5):
     """Kernel times of the rank/grid sweep at h = 5120, N = 131072 on this GPU: r = 16, 64, 128 at
-    G = 20 and r = 32 at G = 40 (config 4; its token-sharded form is this on every rank)."""
+    G = 20 and r = 32 at G = 40 (config 4; its token-sharded form is this on every rank), with the
+    headline's r = 32, G = 20 beside them."""
     h = cfg["h"]
     lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
     gen = torch.Generator(device=dev).manual_seed(555 + rank)
     z = (torch.randn(N, h, generator=gen, device=dev) * cfg["z_std"]).to(torch.bfloat16)
     out = []
-    for r, G in ((16, 20), (64, 20), (128, 20), (32, 40)):
+    for r, G in ((16, 20), (32, 20), (64, 20), (128, 20), (32, 40)):
         C = (torch.randn(h, G + 2, r, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
         go = torch.randn(N, h + r, generator=gen, device=dev).to(torch.bfloat16)
         fwd = lambda: ops.feature_forward(z, C, lo, hi, G, "relu_sq", lam)

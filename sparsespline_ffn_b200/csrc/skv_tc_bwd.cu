@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
   if (tid == 0) {
     mbar_init(gfull, 1);
     for (int i = 0; i < kTStages; ++i) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 1); }
-    for (int i = 0; i < GROUPS; ++i) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 128); }
+    for (int i = 0; i < GROUPS; ++i) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 4); }
     mbar_init(done, 1);
     *abort_flag = 0;
     mbar_init_fence();
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       // (Handing the S columns back two keys earlier, with the loads running two keys ahead in a third
       // register buffer, was measured slower: 1.14 ms against 1.11 ms at the d20 shape.)
       tc_fence_before();
-      mbar_arrive(sempty + grp);
+      mbar_arrive_warp(sempty + grp);
       if (valid) {
         if (P.dz_f32) {
           float* o = reinterpret_cast<float*>(P.dz) + nn * P.dzs + (int64_t)(chunk_begin + ci) * kChunkKeys;
@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(pfull + i, 128);
+      mbar_init(pfull + i, 4);
       mbar_init(pempty + i, 1);
       mbar_init(gfull + i, 1);
       mbar_init(gempty + i, 1);
@@ -496,7 +496,7 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
           have_saved = true;
         }
         fence_async_smem();
-        mbar_arrive(pfull + pg);
+        mbar_arrive_warp(pfull + pg);
       }
     }
     // ---- epilogue: accumulators -> float32 partial of this token split
@@ -720,8 +720,8 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
     mbar_init(tfull, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(sfull + i, 1);
-      mbar_init(sempty + i, 128);
-      mbar_init(pfull + i, 128);
+      mbar_init(sempty + i, 4);
+      mbar_init(pfull + i, 4);
       mbar_init(pempty + i, 1);
     }
     mbar_init(done + 0, 1);
@@ -812,7 +812,7 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
             outv[q] = o;
           }
           tc_fence_before();
-          mbar_arrive(sempty + pg * 2 + (use & 1));
+          mbar_arrive_warp(sempty + pg * 2 + (use & 1));
         }
         if (valid) {
           if (P.dz_f32) {
@@ -906,7 +906,7 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
         else { if (i) sav[0][1] = now; else sav[0][0] = now; }
       }
       fence_async_smem();
-      mbar_arrive(pfull + pg * 2 + st);
+      mbar_arrive_warp(pfull + pg * 2 + st);
     }
   } else {
     reg_dec<kRegsAux>();

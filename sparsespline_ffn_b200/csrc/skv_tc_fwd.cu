@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
   while (tmem_cols < (uint32_t)(GROUPS * r)) tmem_cols <<= 1;
 
   if (tid == 0) {
-    for (int i = 0; i < kStages * GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); }
+    for (int i = 0; i < kStages * GROUPS; ++i) { mbar_init(full + i, 4); mbar_init(empty + i, 1); }
     for (int i = 0; i < kMaxCStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, 1); }
     mbar_init(done, 1);
     *abort_flag = 0;
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
         if (arow) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
       }
       fence_async_smem();
-      mbar_arrive(full + s * GROUPS + grp);
+      mbar_arrive_warp(full + s * GROUPS + grp);
     };
 
     for (int ci = 0; ci < nch; ci += kStages) {
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
   while (tmem_cols < GROUPS * grp_cols) tmem_cols <<= 1;
 
   if (tid == 0) {
-    for (int i = 0; i < 2 * GROUPS; ++i) { mbar_init(full + i, 128); mbar_init(empty + i, 1); }
+    for (int i = 0; i < 2 * GROUPS; ++i) { mbar_init(full + i, 4); mbar_init(empty + i, 1); }
     for (int i = 0; i < GROUPS; ++i) mbar_init(done + i, 1);
     for (int i = 0; i < kMaxTaCStages; ++i) { mbar_init(cfull + i, 1); mbar_init(cempty + i, GROUPS); }
     *abort_flag = 0;
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           tmem_st_words<HLP>(lane_addr + (uint32_t)((half * kHalfKeys + qq) * HLP), Ws[qq]);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(full + grp * 2 + half);
+        mbar_arrive_warp(full + grp * 2 + half);
       }
       if (arow && valid) *reinterpret_cast<uint4*>(arow + ci * kChunkKeys) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
     }
