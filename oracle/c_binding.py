@@ -48,6 +48,11 @@ def lib() -> ctypes.CDLL:
         L.skvo_backward.argtypes = [fp, i64, fp, fp, i64, fp, i64, i64, i32, i32, i32,
                                     f32, f32, f32, i32, fp, dp]
         L.skvo_backward.restype = None
+        L.skvo_forward_o.argtypes = [fp, i64, fp, i64, i32, i32, i32, f32, f32, f32, i32, i32, fp, fp]
+        L.skvo_forward_o.restype = None
+        L.skvo_backward_o.argtypes = [fp, i64, fp, fp, i64, fp, i64, i64, i32, i32, i32,
+                                      f32, f32, f32, i32, i32, fp, dp]
+        L.skvo_backward_o.restype = None
         _lib = L
     return _lib
 
@@ -88,25 +93,26 @@ def knot_index(z32, grid_lo, grid_hi, G) -> np.ndarray:
 
 
 def feature_forward(z32, C32, grid_lo, grid_hi, G, activation_name="relu_sq", lambda_scale=1.0,
-                    want_activation=True):
-    """Returns ``(a [N,h] or None, lambda*delta [N,r])`` as float32."""
+                    want_activation=True, spline_order=2):
+    """Returns ``(a [N,h] or None, lambda*delta [N,r])`` as float32 (``spline_order`` 2: quadratic,
+    L = G + 2; 1: linear, L = G + 1)."""
     z = _f32(z32)
     C = _f32(C32)
     N, h = z.shape
     hC, L, r = C.shape
-    if hC != h or L != G + 2:
+    if hC != h or L != G + spline_order or spline_order not in (1, 2):
         raise ValueError("shape mismatch")
     a = np.empty((N, h), dtype=np.float32) if want_activation else None
     d = np.empty((N, r), dtype=np.float32)
-    lib().skvo_forward(_p(z, ctypes.c_float), h, _p(C, ctypes.c_float), N, h, L, r,
-                       float(np.float32(grid_lo)), _scale(grid_lo, grid_hi, G),
-                       float(lambda_scale), _ACT[activation_name],
-                       _p(a, ctypes.c_float) if a is not None else None, _p(d, ctypes.c_float))
+    lib().skvo_forward_o(_p(z, ctypes.c_float), h, _p(C, ctypes.c_float), N, h, L, r,
+                         float(np.float32(grid_lo)), _scale(grid_lo, grid_hi, G),
+                         float(lambda_scale), _ACT[activation_name], int(spline_order),
+                         _p(a, ctypes.c_float) if a is not None else None, _p(d, ctypes.c_float))
     return a, d
 
 
 def feature_backward(z32, C32, g_delta32, g_a32, grid_lo, grid_hi, G, activation_name="relu_sq",
-                     lambda_scale=1.0):
+                     lambda_scale=1.0, spline_order=2):
     """Returns ``(dz [N,h] float32, dC [h,L,r] float64)``; ``g_a32`` may be None."""
     z = _f32(z32)
     C = _f32(C32)
@@ -116,12 +122,12 @@ def feature_backward(z32, C32, g_delta32, g_a32, grid_lo, grid_hi, G, activation
     _, L, r = C.shape
     dz = np.empty((N, h), dtype=np.float32)
     dC = np.empty((h, L, r), dtype=np.float64)
-    lib().skvo_backward(_p(z, ctypes.c_float), h, _p(C, ctypes.c_float),
-                        _p(gd, ctypes.c_float), r,
-                        _p(ga, ctypes.c_float) if ga is not None else None, h,
-                        N, h, L, r, float(np.float32(grid_lo)), _scale(grid_lo, grid_hi, G),
-                        float(lambda_scale), _ACT[activation_name],
-                        _p(dz, ctypes.c_float), _p(dC, ctypes.c_double))
+    lib().skvo_backward_o(_p(z, ctypes.c_float), h, _p(C, ctypes.c_float),
+                          _p(gd, ctypes.c_float), r,
+                          _p(ga, ctypes.c_float) if ga is not None else None, h,
+                          N, h, L, r, float(np.float32(grid_lo)), _scale(grid_lo, grid_hi, G),
+                          float(lambda_scale), _ACT[activation_name], int(spline_order),
+                          _p(dz, ctypes.c_float), _p(dC, ctypes.c_double))
     return dz, dC
 
 

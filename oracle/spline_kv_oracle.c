@@ -36,7 +36,10 @@ typedef struct {
     float dB[3];      /* derivative weights, clamp mask applied */
 } skvo_basis;
 
-static inline skvo_basis skvo_eval(float z, float lo, float scale, int G)
+/* order 2: quadratic B-spline (rl_spline_kv_reference.py:88-109, three weights at rows bin..bin+2);
+ * order 1: linear B-spline (_b1_basis_and_bins, rl_spline_kv_reference.py:125-142: weights 1-tau and
+ * tau at rows bin, bin+1; the third weight is zero and its row is never read). */
+static inline skvo_basis skvo_eval_o(float z, float lo, float scale, int G, int order)
 {
     skvo_basis o;
     volatile float d = z - lo;            /* keep the two roundings separate */
@@ -54,6 +57,15 @@ static inline skvo_basis skvo_eval(float z, float lo, float scale, int G)
     float m = in_range ? 1.0f : 0.0f;
     float c = clamp_active ? 1.0f : 0.0f;
     o.bin = b;
+    if (order == 1) {
+        o.B[0] = omt * m;
+        o.B[1] = tau * m;
+        o.B[2] = 0.0f;
+        o.dB[0] = -c;
+        o.dB[1] = c;
+        o.dB[2] = 0.0f;
+        return o;
+    }
     o.B[0] = 0.5f * omt * omt * m;
     o.B[1] = 0.5f * (1.0f + 2.0f * tau - 2.0f * tau * tau) * m;
     o.B[2] = 0.5f * tau * tau * m;
@@ -61,6 +73,11 @@ static inline skvo_basis skvo_eval(float z, float lo, float scale, int G)
     o.dB[1] = (1.0f - 2.0f * tau) * c;
     o.dB[2] = tau * c;
     return o;
+}
+
+static inline skvo_basis skvo_eval(float z, float lo, float scale, int G)
+{
+    return skvo_eval_o(z, lo, scale, G, 2);
 }
 
 int skvo_num_threads(void)
@@ -113,10 +130,11 @@ static double skvo_act_grad(float zz, int act)
 
 /* act: 0 = relu_sq, 1 = identity, 2 = gelu.
  * a[N*h] (may be NULL) receives phi(z); delta[N*r] receives lambda * delta. */
-void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, int L, int r,
-                  float lo, float scale, float lambda, int act, float *a, float *delta)
+void skvo_forward_o(const float *z, int64_t zs, const float *C, int64_t N, int h, int L, int r,
+                    float lo, float scale, float lambda, int act, int order, float *a, float *delta)
 {
-    int G = L - 2;
+    int G = L - order;
+    int nb = order + 1;                      /* rows with a weight */
 #pragma omp parallel
     {
         double *acc = (double *)malloc(sizeof(double) * (size_t)r);
@@ -126,11 +144,12 @@ void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, 
             for (int j = 0; j < h; ++j) {
                 float zz = z[n * zs + j];
                 if (a) a[n * h + j] = (float)skvo_act(zz, act);
-                skvo_basis e = skvo_eval(zz, lo, scale, G);
+                skvo_basis e = skvo_eval_o(zz, lo, scale, G, order);
                 const float *row = C + ((size_t)j * L + e.bin) * r;
-                double b0 = e.B[0], b1 = e.B[1], b2 = e.B[2];
-                for (int c = 0; c < r; ++c)
-                    acc[c] += b0 * row[c] + b1 * row[r + c] + b2 * row[2 * r + c];
+                for (int k = 0; k < nb; ++k) {
+                    double bk = e.B[k];
+                    for (int c = 0; c < r; ++c) acc[c] += bk * row[(size_t)k * r + c];
+                }
             }
             for (int c = 0; c < r; ++c) delta[n * r + c] = (float)((double)lambda * acc[c]);
         }
@@ -143,28 +162,28 @@ void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, 
  *   g_a[N*h] (row stride gas) may be NULL (delta-only operator).
  *   dz[N*h] float32 out = g_a*phi'(z) + lambda*dz_spline.
  *   dC[h*L*r] double out = lambda * Phi^T g_delta. */
-void skvo_backward(const float *z, int64_t zs, const float *C,
-                   const float *g_delta, int64_t gds, const float *g_a, int64_t gas,
-                   int64_t N, int h, int L, int r, float lo, float scale, float lambda, int act,
-                   float *dz, double *dC)
+void skvo_backward_o(const float *z, int64_t zs, const float *C,
+                     const float *g_delta, int64_t gds, const float *g_a, int64_t gas,
+                     int64_t N, int h, int L, int r, float lo, float scale, float lambda, int act, int order,
+                     float *dz, double *dC)
 {
-    int G = L - 2;
+    int G = L - order;
+    int nb = order + 1;
     /* dz: parallel over tokens */
 #pragma omp parallel for schedule(static)
     for (int64_t n = 0; n < N; ++n) {
         const float *g = g_delta + n * gds;
         for (int j = 0; j < h; ++j) {
             float zz = z[n * zs + j];
-            skvo_basis e = skvo_eval(zz, lo, scale, G);
+            skvo_basis e = skvo_eval_o(zz, lo, scale, G, order);
             const float *row = C + ((size_t)j * L + e.bin) * r;
-            double s0 = 0.0, s1 = 0.0, s2 = 0.0;
-            for (int c = 0; c < r; ++c) {
-                double gc = g[c];
-                s0 += gc * row[c];
-                s1 += gc * row[r + c];
-                s2 += gc * row[2 * r + c];
+            double sum = 0.0;
+            for (int k = 0; k < nb; ++k) {
+                double sk = 0.0;
+                for (int c = 0; c < r; ++c) sk += (double)g[c] * row[(size_t)k * r + c];
+                sum += e.dB[k] * sk;
             }
-            double v = (double)lambda * (double)scale * (e.dB[0] * s0 + e.dB[1] * s1 + e.dB[2] * s2);
+            double v = (double)lambda * (double)scale * sum;
             if (g_a) {
                 double dphi = skvo_act_grad(zz, act);
                 v += (double)g_a[n * gas + j] * dphi;
@@ -178,17 +197,29 @@ void skvo_backward(const float *z, int64_t zs, const float *C,
         double *slab = dC + (size_t)j * L * r;
         memset(slab, 0, sizeof(double) * (size_t)L * r);
         for (int64_t n = 0; n < N; ++n) {
-            skvo_basis e = skvo_eval(z[n * zs + j], lo, scale, G);
+            skvo_basis e = skvo_eval_o(z[n * zs + j], lo, scale, G, order);
             const float *g = g_delta + n * gds;
             double *row = slab + (size_t)e.bin * r;
-            double b0 = e.B[0], b1 = e.B[1], b2 = e.B[2];
-            for (int c = 0; c < r; ++c) {
-                double gc = g[c];
-                row[c] += b0 * gc;
-                row[r + c] += b1 * gc;
-                row[2 * r + c] += b2 * gc;
+            for (int k = 0; k < nb; ++k) {
+                double bk = e.B[k];
+                for (int c = 0; c < r; ++c) row[(size_t)k * r + c] += bk * (double)g[c];
             }
         }
         for (size_t i = 0; i < (size_t)L * r; ++i) slab[i] *= (double)lambda;
     }
+}
+
+/* The quadratic spline under the names the first version of this file exported. */
+void skvo_forward(const float *z, int64_t zs, const float *C, int64_t N, int h, int L, int r,
+                  float lo, float scale, float lambda, int act, float *a, float *delta)
+{
+    skvo_forward_o(z, zs, C, N, h, L, r, lo, scale, lambda, act, 2, a, delta);
+}
+
+void skvo_backward(const float *z, int64_t zs, const float *C,
+                   const float *g_delta, int64_t gds, const float *g_a, int64_t gas,
+                   int64_t N, int h, int L, int r, float lo, float scale, float lambda, int act,
+                   float *dz, double *dC)
+{
+    skvo_backward_o(z, zs, C, g_delta, gds, g_a, gas, N, h, L, r, lo, scale, lambda, act, 2, dz, dC);
 }

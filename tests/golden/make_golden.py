@@ -10,7 +10,8 @@ It imports the reference's own PyTorch oracle (``flash_spline_feature_reference`
 seeded inputs and stores inputs and outputs in ``spline_kv_golden.npz``; a second
 file, ``module_golden.npz``, holds one forward + backward of the reference's
 ``RLSplineKVReference`` layer per mode (additive, gelu base, no_base, multiplicative
-gate).  The fixtures travel with the repository; the reference does not have to be
+gate), and ``b1_golden.npz`` the linear spline (``spline_order = 1``) of the reference's
+oracle with its autograd gradients.  The fixtures travel with the repository; the reference does not have to be
 present when the tests run.
 """
 from __future__ import annotations
@@ -110,14 +111,61 @@ def module_fixture(reference_src):
     print(path, os.path.getsize(path), "bytes;", len(store), "arrays")
 
 
+def b1_fixture(reference_src):
+    """The linear B-spline (spline_order = 1, L = G + 1) of the reference's PyTorch oracle
+    (rl_spline_kv_reference.py:125-142, 178-187): f and, through autograd, dz and dC, in b1_golden.npz."""
+    sys.path.insert(0, reference_src)
+    from sparsespline_ffn.rl_spline_kv_reference import flash_spline_feature_reference  # noqa: E402
+
+    g = torch.Generator().manual_seed(11)
+
+    def rn(*shape, scale=1.0):
+        return torch.randn(*shape, generator=g, dtype=torch.float32) * scale
+
+    cases = {
+        "uniform": dict(z=rn(48, 24, scale=2.0), C=rn(24, 9, 8, scale=0.1), lo=-3.0, hi=3.0, G=8, act="relu_sq", lam=1.0),
+        "d20_like": dict(z=bf16_round(rn(32, 40, scale=2.5)), C=bf16_round(rn(40, 21, 32, scale=0.02)),
+                         lo=-5.0, hi=5.0, G=20, act="relu_sq", lam=0.25),
+        "gelu": dict(z=rn(36, 24, scale=1.5), C=rn(24, 17, 16, scale=0.1), lo=-4.0, hi=4.0, G=16, act="gelu", lam=0.75),
+    }
+    lo, hi, G = -3.0, 3.0, 12
+    knots = torch.linspace(lo, hi, G + 1, dtype=torch.float32)
+    specials = torch.cat([knots, torch.nextafter(knots, torch.full_like(knots, 10.0)),
+                          torch.nextafter(knots, torch.full_like(knots, -10.0)),
+                          torch.tensor([0.0, -0.0, 100.0, -100.0, 1e30, -1e30, 1e-30], dtype=torch.float32)])
+    cases["edges"] = dict(z=specials[:, None].repeat(1, 4), C=rn(4, G + 1, 8, scale=0.1), lo=lo, hi=hi, G=G,
+                          act="identity", lam=1.0)
+    store = {}
+    for name, c in cases.items():
+        z, C = c["z"], c["C"]
+        N, h = z.shape
+        r = C.shape[-1]
+        go = torch.randn(N, h + r, generator=g, dtype=torch.float32)
+        zt = z.clone().requires_grad_(True)
+        Ct = C.clone().requires_grad_(True)
+        f = flash_spline_feature_reference(zt, Ct, c["lo"], c["hi"], c["G"], activation=c["act"],
+                                           lambda_scale=c["lam"], spline_order=1)
+        f.backward(go)
+        rec = dict(z=z, C=C, go=go, f=f.detach(), dz=zt.grad, dC=Ct.grad,
+                   meta=torch.tensor([c["lo"], c["hi"], float(c["G"]), c["lam"],
+                                      {"relu_sq": 0.0, "identity": 1.0, "gelu": 2.0}[c["act"]]], dtype=torch.float64))
+        for k, v in rec.items():
+            store[f"{name}/{k}"] = v.detach().numpy()
+    path = os.path.join(HERE, "b1_golden.npz")
+    np.savez_compressed(path, **store)
+    print(path, os.path.getsize(path), "bytes;", len(store), "arrays")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference-src", required=True)
-    ap.add_argument("--only", choices=["operator", "module"], help="regenerate one of the two fixture files")
+    ap.add_argument("--only", choices=["operator", "module", "b1"], help="regenerate one of the fixture files")
     args = ap.parse_args()
-    if args.only != "operator":
+    if args.only in (None, "module"):
         module_fixture(args.reference_src)
-    if args.only == "module":
+    if args.only in (None, "b1"):
+        b1_fixture(args.reference_src)
+    if args.only in ("module", "b1"):
         return
     sys.path.insert(0, args.reference_src)
     from sparsespline_ffn.rl_spline_kv_reference import (  # noqa: E402

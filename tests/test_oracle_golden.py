@@ -120,3 +120,37 @@ def test_reference_invariants_hold_for_the_oracle():
     # all tokens far outside the grid => delta exactly 0, finite
     f4 = onp.feature_forward(np.full((N, h), 100.0, np.float32), C, -3, 3, G)
     assert np.all(f4[:, h:] == 0) and np.isfinite(f4).all()
+
+
+# ---------------------------------------------------------------------------------------------
+# linear spline (spline_order = 1): the C oracle against the reference's own outputs
+# ---------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def b1_golden():
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "b1_golden.npz")
+    data = np.load(path)
+    cases = {}
+    for key in data.files:
+        case, name = key.split("/")
+        cases.setdefault(case, {})[name] = data[key]
+    return cases
+
+
+@pytest.mark.parametrize("case", ["uniform", "d20_like", "gelu", "edges"])
+def test_c_oracle_linear_spline_matches_the_reference(b1_golden, case):
+    from oracle import c_binding as oc
+    c = b1_golden[case]
+    lo, hi, G, lam = float(c["meta"][0]), float(c["meta"][1]), int(c["meta"][2]), float(c["meta"][3])
+    act = {0: "relu_sq", 1: "identity", 2: "gelu"}[int(c["meta"][4])]
+    z, C, go = c["z"], c["C"], c["go"]
+    h = z.shape[1]
+    a, d = oc.feature_forward(z, C, lo, hi, G, act, lam, spline_order=1)
+    f_ref = c["f"]
+    finite = np.isfinite(z)
+    np.testing.assert_allclose(a[finite], f_ref[:, :h][finite], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(d, f_ref[:, h:], rtol=1e-4, atol=1e-6)
+    dz, dC = oc.feature_backward(z, C, go[:, h:], go[:, :h], lo, hi, G, act, lam, spline_order=1)
+    np.testing.assert_allclose(dz[finite], c["dz"][finite], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(dC, c["dC"], rtol=1e-4, atol=1e-5)
+    assert not dC[:, -1].any()                      # the last knot row never gets a weight
