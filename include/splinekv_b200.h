@@ -6,7 +6,8 @@
  *   backward   dz = g_a * phi'(z) + lambda * scale * sum_k B_k'(z) <g_delta, C[j, bin+k, :]>
  *              dC = lambda * Phi(z)^T g_delta
  *
- * z is [N, h] (tokens x keys), C is [h, L, r] with L = G + 2 knot rows, outputs are in
+ * z is [N, h] (tokens x keys), C is [h, L, r] with L = G + 2 knot rows (G + 1 for the linear
+ * spline, skv_problem.spline_order), outputs are in
  * the dtype of z.  Every entry point takes plain device pointers, sizes and a CUDA stream
  * handle (cudaStream_t passed as void*); none of them allocates, frees, synchronises or
  * throws.  They enqueue work on the given stream and return 0 or a negative SKV_ERR_* code.
@@ -24,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SKV_ABI_VERSION 2
+#define SKV_ABI_VERSION 3
 
 enum skv_error {
   SKV_OK = 0,
@@ -66,6 +67,10 @@ typedef struct skv_problem {
   int32_t dz_f32;      /* backward only, tcgen05 kernels: 1 = write dz as float32 (before its rounding
                           to the dtype of z), so that a systematic error of dz can be measured; the
                           dz pointer and stride are then in float32 elements */
+  int32_t spline_order; /* 0 or 2: quadratic B-spline, L = G + 2 (the operator of the reference's kernels);
+                          1: linear B-spline, L = G + 1, weights 1 - tau and tau at rows bin, bin + 1
+                          (_b1_basis_and_bins, src/sparsespline_ffn/rl_spline_kv_reference.py:125-142, which the
+                          reference evaluates in PyTorch only); runs on the CUDA-core kernels */
 } skv_problem;
 
 /* ABI version of the loaded library (SKV_ABI_VERSION). */

@@ -27,7 +27,7 @@ class Problem(ctypes.Structure):
         ("N", ctypes.c_int64), ("h", ctypes.c_int32), ("L", ctypes.c_int32), ("r", ctypes.c_int32),
         ("grid_lo", ctypes.c_float), ("scale", ctypes.c_float), ("lambda_scale", ctypes.c_float),
         ("activation", ctypes.c_int32), ("dtype", ctypes.c_int32), ("impl", ctypes.c_int32),
-        ("delta_f32", ctypes.c_int32), ("dz_f32", ctypes.c_int32),
+        ("delta_f32", ctypes.c_int32), ("dz_f32", ctypes.c_int32), ("spline_order", ctypes.c_int32),
     ]
 
 
@@ -72,7 +72,7 @@ def load() -> ctypes.CDLL:
     lib.skv_feature_forward_noalloc.restype = i32
     lib.skv_debug_set.argtypes = [i32, i64]
     lib.skv_debug_set.restype = i32
-    if lib.skv_abi_version() != 2:
+    if lib.skv_abi_version() != 3:
         raise RuntimeError("libsplinekv_b200.so has an unexpected ABI version; rebuild it")
     _lib = lib
     return lib

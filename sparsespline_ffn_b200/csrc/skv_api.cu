@@ -26,7 +26,7 @@ namespace {
 
 int validate(const skv_problem* p) {
   if (!p) return SKV_ERR_NULL;
-  if (p->N < 0 || p->h < 1 || p->L < 4 || p->r < 1) return SKV_ERR_SHAPE;
+  if (p->N < 0 || p->h < 1 || p->L < (p->spline_order == 1 ? 3 : 4) || p->r < 1) return SKV_ERR_SHAPE;
   if (p->N > (int64_t)1 << 40 || p->h > (1 << 24) || p->L > 4096) return SKV_ERR_SHAPE;
   if (p->dtype != SKV_BF16 && p->dtype != SKV_F32) return SKV_ERR_UNSUPPORTED;
   if (p->activation != SKV_ACT_RELU_SQ && p->activation != SKV_ACT_IDENTITY && p->activation != SKV_ACT_GELU)
@@ -34,12 +34,13 @@ int validate(const skv_problem* p) {
   if (p->impl != SKV_IMPL_AUTO && p->impl != SKV_IMPL_SIMT && p->impl != SKV_IMPL_TCGEN05)
     return SKV_ERR_UNSUPPORTED;
   if (p->r > 256) return SKV_ERR_UNSUPPORTED;
+  if (p->spline_order != 0 && p->spline_order != 1 && p->spline_order != 2) return SKV_ERR_UNSUPPORTED;
   return SKV_OK;
 }
 
 int resolve(const skv_problem& p) {
   if (p.impl == SKV_IMPL_SIMT) return SKV_IMPL_SIMT;
-  const bool ok = tc_eligible(p);
+  const bool ok = p.spline_order != 1 && tc_eligible(p);      // the linear spline runs on the CUDA-core kernels
   if (p.impl == SKV_IMPL_TCGEN05) return ok ? (int)SKV_IMPL_TCGEN05 : (int)SKV_ERR_UNSUPPORTED;
   return ok ? (int)SKV_IMPL_TCGEN05 : (int)SKV_IMPL_SIMT;
 }
@@ -73,11 +74,13 @@ int make_ctx(const skv_problem* p, void* stream, int32_t* status, LaunchCtx* c) 
   int sms = 0;
   if (int e = device_info(&sms)) return e;
   c->p = *p;
-  c->G = p->L - 2;
+  const int order = p->spline_order == 1 ? 1 : 2;
+  c->G = p->L - order;
   c->g.lo = p->grid_lo;
   c->g.scale = p->scale;
-  c->g.Gf = (float)(p->L - 2);
-  c->g.Gm1f = (float)(p->L - 3);
+  c->g.Gf = (float)(p->L - order);
+  c->g.Gm1f = (float)(p->L - order - 1);
+  c->g.order = order;
   c->stream = (cudaStream_t)stream;
   c->status = status;
   c->num_sms = sms;
@@ -98,7 +101,7 @@ const char* skv_error_string(int code) {
   switch (code) {
     case SKV_OK: return "ok";
     case SKV_ERR_NULL: return "a required pointer is NULL";
-    case SKV_ERR_SHAPE: return "bad shape: need N >= 0, h >= 1, L = G + 2 >= 4, r >= 1";
+    case SKV_ERR_SHAPE: return "bad shape: need N >= 0, h >= 1, L = G + spline_order with G >= 2, r >= 1";
     case SKV_ERR_UNSUPPORTED: return "unsupported dtype, activation, impl or r > 256 for this shape";
     case SKV_ERR_ALIGN: return "pointer or stride alignment required by the kernel is not met";
     case SKV_ERR_SCRATCH: return "scratch buffer missing or smaller than skv_scratch_bytes()";

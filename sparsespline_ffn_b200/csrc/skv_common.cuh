@@ -18,6 +18,7 @@ struct GridParams {
   float scale;   // float32(G / (hi - lo))
   float Gf;      // (float)G
   float Gm1f;    // (float)(G - 1)
+  int order;     // 2: quadratic B-spline (three weights per pair); 1: linear (two)
 };
 
 // Knot interval and local coordinate of one pre-activation value.
@@ -60,18 +61,22 @@ __device__ __forceinline__ Knot knot_of(float z, const GridParams& g) {
 }
 
 // Forward weights B_0..B_2 (rl_spline_kv_reference.py:105-108), forward mask applied.
-__device__ __forceinline__ void basis_weights(const Knot& k, float& B0, float& B1, float& B2) {
+// order 1: the linear spline's 1 - tau and tau (rl_spline_kv_reference.py:139-141); B2 stays zero
+// and its row must not be touched (it lies past the key's L = G + 1 rows).
+__device__ __forceinline__ void basis_weights(const Knot& k, float& B0, float& B1, float& B2, int order = 2) {
   float t = k.tau, omt = 1.0f - t;
   float m = k.in_range ? 1.0f : 0.0f;
+  if (order == 1) { B0 = omt * m; B1 = t * m; B2 = 0.0f; return; }
   B0 = 0.5f * omt * omt * m;
   B1 = 0.5f * (1.0f + 2.0f * t - 2.0f * t * t) * m;
   B2 = 0.5f * t * t * m;
 }
 
 // Derivative weights dB_k/dtau (flash_spline_feature_backward_ref.py:64-66), clamp mask applied.
-__device__ __forceinline__ void basis_derivs(const Knot& k, float& d0, float& d1, float& d2) {
+__device__ __forceinline__ void basis_derivs(const Knot& k, float& d0, float& d1, float& d2, int order = 2) {
   float t = k.tau;
   float m = k.clamp_active ? 1.0f : 0.0f;
+  if (order == 1) { d0 = -m; d1 = m; d2 = 0.0f; return; }
   d0 = -(1.0f - t) * m;
   d1 = (1.0f - 2.0f * t) * m;
   d2 = t * m;

@@ -33,6 +33,7 @@ simt_forward_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict__ C
   const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp, nwarps = blockDim.x / kWarp;
   const int64_t n0 = (int64_t)blockIdx.x * TB;
   const int riter = (r + kWarp - 1) / kWarp;
+  const bool three = g.order != 1;                    // the linear spline has no third row
 
   for (int i = threadIdx.x; i < TB * r; i += blockDim.x) dacc[i] = 0.0f;
 
@@ -56,7 +57,7 @@ simt_forward_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict__ C
         if (jl < kc) {
           float zz = ld_f32<T>(z + n * zs + j0 + jl);
           Knot k = knot_of(zz, g);
-          basis_weights(k, B0, B1, B2);
+          basis_weights(k, B0, B1, B2, g.order);
           bin = k.bin;
           if (act_out) st_f32<T>(act_out + n * as + j0 + jl, act_fwd(zz, act));
         }
@@ -71,7 +72,7 @@ simt_forward_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict__ C
           for (int ci = 0; ci < kMaxRIter; ++ci) {
             if (ci < riter) {
               const int c = ci * kWarp + lane;
-              if (c < r) acc[ci] += w0 * row[c] + w1 * row[r + c] + w2 * row[2 * r + c];
+              if (c < r) acc[ci] += w0 * row[c] + w1 * row[r + c] + (three ? w2 * row[2 * r + c] : 0.0f);
             }
           }
         }
@@ -110,6 +111,7 @@ simt_dz_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict__ C,
   const int64_t n0 = (int64_t)blockIdx.x * TB;
   const int riter = (r + kWarp - 1) / kWarp;
   const float coef = lambda * g.scale;
+  const bool three = g.order != 1;
 
   for (int j0 = 0; j0 < h; j0 += KCH) {
     const int kc = min(KCH, h - j0);
@@ -134,7 +136,7 @@ simt_dz_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict__ C,
         if (jl < kc) {
           zz = ld_f32<T>(z + n * zs + j0 + jl);
           Knot k = knot_of(zz, g);
-          basis_derivs(k, d0, d1, d2);
+          basis_derivs(k, d0, d1, d2, g.order);
           bin = k.bin;
         }
         float v[kWarp];
@@ -152,7 +154,7 @@ simt_dz_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict__ C,
             for (int ci = 0; ci < kMaxRIter; ++ci) {
               if (ci < riter) {
                 const int c = ci * kWarp + lane;
-                if (c < r) p += gd[ci] * (w0 * row[c] + w1 * row[r + c] + w2 * row[2 * r + c]);
+                if (c < r) p += gd[ci] * (w0 * row[c] + w1 * row[r + c] + (three ? w2 * row[2 * r + c] : 0.0f));
               }
             }
           }
@@ -201,6 +203,7 @@ simt_dc_partial_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict_
   const int64_t ne = min(N, nb + tokens_per_split);
   const int riter = (r + kWarp - 1) / kWarp;
 
+  const bool three = g.order != 1;
   for (int i = threadIdx.x; i < KD * L * r; i += blockDim.x) acc[i] = 0.0f;
   float* my = acc + (size_t)warp * L * r;
 
@@ -220,7 +223,7 @@ simt_dc_partial_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict_
         float B0 = 0.f, B1 = 0.f, B2 = 0.f;
         if (tg + lane < tt) {
           Knot k = knot_of(zt[(tg + lane) * KD + warp], g);
-          basis_weights(k, B0, B1, B2);
+          basis_weights(k, B0, B1, B2, g.order);
           bin = k.bin;
         }
         const int cnt = min(kWarp, tt - tg);
@@ -237,7 +240,7 @@ simt_dc_partial_kernel(const T* __restrict__ z, int64_t zs, const T* __restrict_
               const float gv = gr[c];
               row[c] += w0 * gv;
               row[r + c] += w1 * gv;
-              row[2 * r + c] += w2 * gv;
+              if (three) row[2 * r + c] += w2 * gv;
             }
           }
         }

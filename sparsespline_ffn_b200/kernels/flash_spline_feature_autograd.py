@@ -93,10 +93,44 @@ class FlashSplineFeature(torch.autograd.Function):
         return (dz, _capture_safe_dC_return(C, dC), None, None, None, None, None, None, None, None)
 
 
+class SplineFeatureOfOrder(torch.autograd.Function):
+    """``[phi(z); lambda * delta(z, C)]`` for a spline order given explicitly.  The reference's
+    operators have no such argument (they are the quadratic spline; its linear spline,
+    ``spline_order=1`` of ``flash_spline_feature_reference``, src/sparsespline_ffn/rl_spline_kv_reference.py:178-187,
+    runs in PyTorch only), so this is a separate Function and :class:`FlashSplineFeature` keeps the
+    reference's argument list."""
+
+    @staticmethod
+    def forward(ctx, z, C, grid_lo, grid_hi, G, activation, lambda_scale, spline_order):
+        _require_kernel(True, z)
+        f = ops.feature_forward(z.detach(), C.detach(), grid_lo, grid_hi, G, activation, lambda_scale,
+                                with_base=True, spline_order=spline_order)
+        ctx.save_for_backward(z, C)
+        ctx.cfg = (float(grid_lo), float(grid_hi), int(G), activation, float(lambda_scale), int(spline_order))
+        return f
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        z, C = ctx.saved_tensors
+        lo, hi, G, act, lam, order = ctx.cfg
+        need_dz, need_dC = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dz, dC32, dC_cast = ops.feature_backward(z.detach(), C.detach(), grad_output, lo, hi, G, act, lam,
+                                                 with_base=True, need_dz=need_dz, need_dC=need_dC,
+                                                 spline_order=order)
+        dC = None
+        if need_dC:
+            dC = dC_cast if dC_cast is not None else dC32.to(C.dtype)
+        return (dz, _capture_safe_dC_return(C, dC), None, None, None, None, None, None)
+
+
 def flash_spline_feature(z, C, grid_lo=-3.0, grid_hi=3.0, G=20, activation="relu_sq", lambda_scale=1.0,
-                         use_kernel=True, bwd_kernel="triton", fwd_kernel="auto"):
+                         use_kernel=True, bwd_kernel="triton", fwd_kernel="auto", spline_order=2):
     """Functional form of :class:`FlashSplineFeature` (same defaults as the reference's wrapper,
-    flash_spline_feature_autograd.py:269-292)."""
+    flash_spline_feature_autograd.py:269-292).  ``spline_order=1`` (not an argument of the reference's
+    wrapper) selects the linear B-spline through :class:`SplineFeatureOfOrder`."""
+    if spline_order != 2:
+        _require_kernel(use_kernel, z)
+        return SplineFeatureOfOrder.apply(z, C, grid_lo, grid_hi, G, activation, lambda_scale, spline_order)
     return FlashSplineFeature.apply(z, C, grid_lo, grid_hi, G, activation, lambda_scale, use_kernel,
                                     bwd_kernel, fwd_kernel)
 
@@ -137,4 +171,5 @@ def flash_spline_delta(z, C, grid_lo=-3.0, grid_hi=3.0, G=20, lambda_scale=1.0, 
     return FlashSplineDelta.apply(z, C, grid_lo, grid_hi, G, lambda_scale, bwd_kernel)
 
 
-__all__ = ["FlashSplineFeature", "flash_spline_feature", "FlashSplineDelta", "flash_spline_delta"]
+__all__ = ["FlashSplineFeature", "flash_spline_feature", "FlashSplineDelta", "flash_spline_delta",
+           "SplineFeatureOfOrder"]

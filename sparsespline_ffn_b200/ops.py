@@ -40,7 +40,8 @@ def check_status(device: torch.device) -> None:
         raise RuntimeError(f"splinekv_b200 kernel reported device status {v:#x} (a bounded wait ran out)")
 
 
-def _problem(z: torch.Tensor, C: torch.Tensor, grid_lo, grid_hi, G, activation, lambda_scale, impl) -> _lib.Problem:
+def _problem(z: torch.Tensor, C: torch.Tensor, grid_lo, grid_hi, G, activation, lambda_scale, impl,
+             spline_order: int = 2) -> _lib.Problem:
     if z.dim() != 2:
         raise ValueError(f"z must be 2D [N, h], got {tuple(z.shape)}")
     if C.dim() != 3:
@@ -49,8 +50,10 @@ def _problem(z: torch.Tensor, C: torch.Tensor, grid_lo, grid_hi, G, activation, 
     hC, L, r = C.shape
     if hC != h:
         raise ValueError(f"C[0]={hC} != h={h}")
-    if L != G + 2:
-        raise ValueError(f"L={L} should equal G+spline_order={G + 2}")
+    if spline_order not in (1, 2):
+        raise ValueError(f"spline_order must be 1 or 2; got {spline_order}")
+    if L != G + spline_order:
+        raise ValueError(f"L={L} should equal G+spline_order={G + spline_order}")
     if not float(grid_hi) > float(grid_lo):
         raise ValueError(f"grid_hi {grid_hi} <= grid_lo {grid_lo}")
     if activation not in _lib.SKV_ACT:
@@ -66,7 +69,7 @@ def _problem(z: torch.Tensor, C: torch.Tensor, grid_lo, grid_hi, G, activation, 
         raise RuntimeError(f"unsupported dtype {z.dtype}: the sm_100a kernels take bfloat16 or float32")
     return _lib.Problem(N=N, h=h, L=L, r=r, grid_lo=float(grid_lo), scale=grid_scale(grid_lo, grid_hi, G),
                         lambda_scale=float(lambda_scale), activation=_lib.SKV_ACT[activation],
-                        dtype=_DTYPES[z.dtype], impl=_lib.SKV_IMPL[impl])
+                        dtype=_DTYPES[z.dtype], impl=_lib.SKV_IMPL[impl], spline_order=int(spline_order))
 
 
 _warned_slow: set[tuple] = set()
@@ -131,15 +134,16 @@ def resolve_impl(z, C, grid_lo, grid_hi, G, impl="auto") -> str:
 
 
 def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0, with_base=True,
-                    impl="auto", out: torch.Tensor | None = None, delta_f32: bool = False):
+                    impl="auto", out: torch.Tensor | None = None, delta_f32: bool = False, spline_order: int = 2):
     """``[phi(z); lambda*delta]`` as ``[N, h+r]`` (``with_base``) or ``lambda*delta`` as ``[N, r]``.
 
     With ``delta_f32`` the residual comes back in float32 whatever the dtype of ``z`` (the
     key-sharded mode sums partial residuals across GPUs before the one rounding to bf16); the two
-    halves then cannot share a tensor, so the result is ``(phi(z) or None, delta_f32)``."""
+    halves then cannot share a tensor, so the result is ``(phi(z) or None, delta_f32)``.
+    ``spline_order=1`` selects the linear B-spline (``C`` is ``[h, G + 1, r]``; CUDA-core kernels)."""
     lib = _lib.load()
     C = C.to(z.dtype) if C.dtype != z.dtype else C
-    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, impl)
+    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, impl, spline_order)
     z = _rows(z)
     C = C.contiguous()
     N, h, r = p.N, p.h, p.r
@@ -172,7 +176,8 @@ def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scal
 
 
 def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0,
-                     with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True, dz_f32=False):
+                     with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True, dz_f32=False,
+                     spline_order: int = 2):
     """Gradients for ``grad_out`` of :func:`feature_forward`: one ``[N, h+r]`` (or ``[N, r]``) tensor,
     consumed in place through a base pointer and a row stride per half, or a ``(g_act, g_delta)``
     pair of separate tensors.
@@ -185,7 +190,7 @@ def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", 
     lib = _lib.load()
     C_in_dtype = C.dtype
     C = C.to(z.dtype) if C.dtype != z.dtype else C
-    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, impl)
+    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, impl, spline_order)
     z = _rows(z)
     C = C.contiguous()
     N, h, r, L = p.N, p.h, p.r, p.L

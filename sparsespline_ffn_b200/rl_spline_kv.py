@@ -12,8 +12,8 @@ reference module loads, and the same three forward graphs:
 
 What differs, on purpose: the operator always runs on the sm_100a kernels (there is no eager path, so
 ``use_kernel`` is accepted and must not be asked to be False on this package's behalf: a CPU input
-raises), ``spline_order = 1`` is refused (the reference's operators do not take it either,
-``:351-352``), and the per-forward diagnostics of the reference (``:376-481``) are not computed, which
+raises), ``spline_order = 1`` (the linear spline, additive mode only, as in the reference, ``:303, 323``)
+runs on the library's CUDA-core kernels instead of PyTorch code, and the per-forward diagnostics of the reference (``:376-481``) are not computed, which
 also removes the host synchronisations they cause.  The two GEMMs around the operator are
 ``torch.nn.Linear``.
 """
@@ -25,7 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .kernels.flash_spline_feature_autograd import FlashSplineDelta, FlashSplineFeature
+from .kernels.flash_spline_feature_autograd import FlashSplineDelta, FlashSplineFeature, SplineFeatureOfOrder
 
 
 @dataclass
@@ -89,8 +89,8 @@ class RLSplineKV(nn.Module):
         tensor-core kernels under float32 master weights and GEMMs; None keeps the dtype of ``K x``."""
         super().__init__()
         self.operator_dtype = operator_dtype
-        if cfg.spline_order != 2:
-            raise NotImplementedError("the sm_100a operators implement the quadratic (order 2) spline only")
+        if cfg.spline_order != 2 and (cfg.no_base or cfg.gating_mode == "multiplicative"):
+            raise NotImplementedError("no_base and multiplicative gating require spline_order=2")
         self.cfg = cfg
         d = cfg.d
         h = max(1, int(d * cfg.h_ratio))
@@ -144,6 +144,9 @@ class RLSplineKV(nn.Module):
         elif cfg.gating_mode == "multiplicative":
             delta = FlashSplineDelta.apply(z, C, lo, hi, G, lam, cfg.bwd_kernel)              # [N, r], carries lambda
             y = self.W_out((1.0 + self.W_d_proj(delta.to(out_dtype))) * _phi(z_full, cfg.activation))
+        elif cfg.spline_order == 1:
+            f = SplineFeatureOfOrder.apply(z, C, lo, hi, G, cfg.activation, lam, 1)            # [N, h + r]
+            y = self.W_out(f.to(out_dtype))
         else:
             f = FlashSplineFeature.apply(z, C, lo, hi, G, cfg.activation, lam, True, cfg.bwd_kernel,
                                          cfg.fwd_kernel)                                       # [N, h + r]

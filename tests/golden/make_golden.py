@@ -76,6 +76,7 @@ MODULE_CASES = {
     "additive_gelu": dict(activation="gelu"),
     "no_base": dict(no_base=True),
     "multiplicative": dict(gating_mode="multiplicative"),
+    "additive_linear": dict(spline_order=1),
 }
 
 
@@ -161,6 +162,7 @@ def main():
     ap.add_argument("--reference-src", required=True)
     ap.add_argument("--only", choices=["operator", "module", "b1"], help="regenerate one of the fixture files")
     args = ap.parse_args()
+    torch.set_num_threads(1)          # the reference's scatter-add backward is order-dependent across threads
     if args.only in (None, "module"):
         module_fixture(args.reference_src)
     if args.only in (None, "b1"):

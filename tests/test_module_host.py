@@ -30,9 +30,12 @@ def test_parameter_names_and_shapes(mode, readout_in):
     assert m.num_params() == sum(p.numel() for p in m.parameters())
 
 
-def test_linear_spline_is_refused_and_cpu_input_raises():
+def test_linear_spline_modes_and_cpu_input():
+    assert tuple(RLSplineKV(RLSplineKVConfig(d=16, r=8, spline_order=1)).C.shape) == (16, 21, 8)   # L = G + 1
     with pytest.raises(NotImplementedError):
-        RLSplineKV(RLSplineKVConfig(d=16, spline_order=1))
+        RLSplineKV(RLSplineKVConfig(d=16, spline_order=1, no_base=True))
+    with pytest.raises(NotImplementedError):
+        RLSplineKV(RLSplineKVConfig(d=16, spline_order=1, gating_mode="multiplicative"))
     m = RLSplineKV(RLSplineKVConfig(d=16, r=8))
     with pytest.raises(RuntimeError, match="CUDA-only"):
         m(torch.randn(4, 16))
