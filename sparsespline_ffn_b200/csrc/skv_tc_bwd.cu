@@ -1172,11 +1172,11 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
   if (cudaMemsetAsync(amax, 0, 256, c.stream) != cudaSuccess) return SKV_ERR_LAUNCH;
   {
     const int64_t total = p.N * p.r;
-    const unsigned grid = (unsigned)((total + 1023) / 1024 < 1184 ? (total + 1023) / 1024 : 1184);
+    const unsigned grid = (unsigned)((total + 2047) / 2048 < 296 ? (total + 2047) / 2048 : 296);
     tc_amax_kernel<<<grid, 256, 0, c.stream>>>((const __nv_bfloat16*)g_delta, gds, p.N, p.r, amax + kAmaxG);
     if (dz) {
       const int64_t crows = (int64_t)p.h * p.L;
-      const unsigned cgrid = (unsigned)((crows * p.r + 1023) / 1024 < 1184 ? (crows * p.r + 1023) / 1024 : 1184);
+      const unsigned cgrid = (unsigned)((crows * p.r + 2047) / 2048 < 296 ? (crows * p.r + 2047) / 2048 : 296);
       tc_amax_kernel<<<cgrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, p.r, crows, p.r, amax + kAmaxC);
       note_launches(1);
     }

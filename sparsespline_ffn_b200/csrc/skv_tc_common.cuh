@@ -286,8 +286,16 @@ __global__ void tc_amax_kernel(const __nv_bfloat16* __restrict__ a, int64_t stri
       if (v == v) m = max(m, __float_as_uint(v));
     }
   }
+  // one atomic per CTA: thousands of per-warp atomics on one word serialise in L2
+  __shared__ uint32_t wmax[32];
   for (int s = 16; s >= 1; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
-  if ((threadIdx.x & 31) == 0 && m) atomicMax(amax_bits, m);
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = threadIdx.x < (blockDim.x + 31) / 32 ? wmax[threadIdx.x] : 0u;
+    for (int s = 16; s >= 1; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+    if (threadIdx.x == 0 && m) atomicMax(amax_bits, m);
+  }
 }
 }  // namespace
 

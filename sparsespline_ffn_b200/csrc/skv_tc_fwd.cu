@@ -620,7 +620,7 @@ size_t fwd_scratch_bytes(const skv_problem& p) {
 int launch_pack_c(const LaunchCtx& c, const void* C, uint32_t* hdr, void* img, int LP) {
   if (cudaMemsetAsync(hdr, 0, 256, c.stream) != cudaSuccess) return SKV_ERR_LAUNCH;
   const int64_t crows = (int64_t)c.p.h * c.p.L;
-  const unsigned agrid = (unsigned)((crows * c.p.r + 1023) / 1024 < 1184 ? (crows * c.p.r + 1023) / 1024 : 1184);
+  const unsigned agrid = (unsigned)((crows * c.p.r + 2047) / 2048 < 296 ? (crows * c.p.r + 2047) / 2048 : 296);
   tc_amax_kernel<<<agrid, 256, 0, c.stream>>>((const __nv_bfloat16*)C, c.p.r, crows, c.p.r, hdr + kAmaxC);
   const size_t pieces = (size_t)c.p.h * LP * (c.p.r / 8);
   const unsigned grid = (unsigned)((pieces + 255) / 256 < 2048 ? (pieces + 255) / 256 : 2048);
