@@ -281,8 +281,8 @@ def test_small_code_table_magnitudes(c_scale):
     ops.check_status(z.device)
 
 
-@pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] % 16 == 0 and s[2] <= 32 and s[3] <= 22 and s[3] % 2 == 0],
-                         ids=_sid)
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] % 16 == 0 and s[2] <= 32 and s[3] <= 22 and s[3] % 2 == 0]
+                         + [(1, 16, 16, 22), (129, 32, 32, 22), (385, 48, 32, 10)], ids=_sid)
 def test_fused_backward_matches_the_two_kernel_backward(shape):
     """The one-kernel form of the backward (dz and dC roles in one CTA) against the default two
     kernels and the oracle: dz bit for bit, dC up to the order of the token sum."""
