@@ -54,7 +54,7 @@ enum skv_op { SKV_OP_FORWARD = 0, SKV_OP_BACKWARD = 1 };
 typedef struct skv_problem {
   int64_t N;           /* tokens */
   int32_t h;           /* keys */
-  int32_t L;           /* knot rows per key, = G + 2 */
+  int32_t L;           /* knot rows per key, = G + 2 (G + 1 when spline_order is 1) */
   int32_t r;           /* code dimension */
   float grid_lo;
   float scale;
