@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SKV_ABI_VERSION 3
+#define SKV_ABI_VERSION 4
 
 enum skv_error {
   SKV_OK = 0,
@@ -129,6 +129,24 @@ int skv_feature_backward(const skv_problem *p, const void *z, int64_t z_stride, 
  * function all kernels use.  Lets a caller check indices bit for bit against
  * _b2_basis_and_bins (src/sparsespline_ffn/rl_spline_kv_reference.py:88-109). */
 int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_t *bins, void *stream);
+
+/* Feature followed by its read-out projection, without the feature tensor in between:
+ *   y[N, d_out] = phi(z) . W_out[:, 0:h]^T + (lambda * delta(z, C)) . W_out[:, h:h+r]^T
+ * Replaces spline_kv_fwd_fused_cuda (src/sparsespline_ffn/cuda_ext/spline_kv_fwd.cu:307-417, wrapper
+ * src/sparsespline_ffn/cuda_ext/__init__.py:617-647), which writes phi(z) and delta to memory and calls two
+ * library GEMMs.  Here delta comes from the feature kernels in their delta-only mode and one tcgen05 GEMM
+ * over K = h + r applies phi to the z tile on its way into shared memory; phi(z) and delta are rounded to
+ * bf16 before the product and the accumulation is float32, as in the reference.  Forward only, like the
+ * reference's entry point.
+ *   w_out    [d_out, h + r] bf16, row stride w_stride elements (the layout of torch.nn.Linear.weight)
+ *   y        [N, d_out] bf16 out, row stride y_stride
+ * Needs dtype bf16, activation relu_sq or identity, h, r, d_out, the three row strides multiples of 8 and
+ * 16-byte aligned pointers (else SKV_ERR_UNSUPPORTED / SKV_ERR_ALIGN).  Scratch:
+ * skv_readout_scratch_bytes(p, d_out).  A bounded wait of the GEMM that runs out sets bit 0x10 of *status. */
+size_t skv_readout_scratch_bytes(const skv_problem *p, int64_t d_out);
+int skv_feature_readout_forward(const skv_problem *p, const void *z, int64_t z_stride, const void *C,
+                                const void *w_out, int64_t w_stride, int64_t d_out, void *y, int64_t y_stride,
+                                void *scratch, size_t scratch_bytes, int32_t *status, void *stream);
 
 /* Forward for callers that cannot allocate device memory (no counterpart in the reference, whose
  * kernels allocate their scratch themselves through the PyTorch allocator).  Same arguments and

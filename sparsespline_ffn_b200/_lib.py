@@ -15,7 +15,7 @@ SKV_OP_FORWARD, SKV_OP_BACKWARD = 0, 1
 EXPORTS = (
     "skv_abi_version", "skv_error_string", "skv_device_ok", "skv_resolve_impl", "skv_scratch_bytes",
     "skv_feature_forward", "skv_feature_backward", "skv_knot_index", "skv_kernel_launches",
-    "skv_feature_forward_noalloc", "skv_debug_set",
+    "skv_feature_forward_noalloc", "skv_debug_set", "skv_readout_scratch_bytes", "skv_feature_readout_forward",
 )
 SKV_DEBUG_WAIT_CYCLES, SKV_DEBUG_SKIP_FIRST_COPY, SKV_DEBUG_FUSED_BACKWARD = 0, 1, 2
 SKV_NOALLOC_SCRATCH_BYTES = 16 << 20
@@ -72,7 +72,11 @@ def load() -> ctypes.CDLL:
     lib.skv_feature_forward_noalloc.restype = i32
     lib.skv_debug_set.argtypes = [i32, i64]
     lib.skv_debug_set.restype = i32
-    if lib.skv_abi_version() != 3:
+    lib.skv_readout_scratch_bytes.argtypes = [pp, i64]
+    lib.skv_readout_scratch_bytes.restype = ctypes.c_size_t
+    lib.skv_feature_readout_forward.argtypes = [pp, vp, i64, vp, vp, i64, i64, vp, i64, vp, ctypes.c_size_t, vp, vp]
+    lib.skv_feature_readout_forward.restype = i32
+    if lib.skv_abi_version() != 4:
         raise RuntimeError("libsplinekv_b200.so has an unexpected ABI version; rebuild it")
     _lib = lib
     return lib

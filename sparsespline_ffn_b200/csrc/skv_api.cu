@@ -22,7 +22,19 @@ int fused_backward_roles() { return g_fused_bwd.load(std::memory_order_relaxed);
 }  // namespace tc
 }  // namespace skv
 
+namespace skv {
+namespace tc {
+bool readout_eligible(const skv_problem& p, int64_t D);
+size_t readout_image_bytes(const skv_problem& p, int64_t D);
+int64_t readout_delta_pitch(const skv_problem& p);
+int readout(const LaunchCtx& c, const void* z, int64_t zs, const void* delta, const void* W, int64_t ws, int64_t D,
+            void* y, int64_t ys, void* wimg);
+}  // namespace tc
+}  // namespace skv
+
 namespace {
+
+size_t round256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 int validate(const skv_problem* p) {
   if (!p) return SKV_ERR_NULL;
@@ -208,6 +220,40 @@ int skv_feature_backward(const skv_problem* p, const void* z, int64_t z_stride, 
   }
   return simt_backward(c, z, z_stride, C, g_act, gact_stride, g_delta, gdelta_stride, dz, dz_stride, dC_f32,
                        dC_cast, scratch, scratch_bytes);
+}
+
+size_t skv_readout_scratch_bytes(const skv_problem* p, int64_t d_out) {
+  if (validate(p) != SKV_OK || !tc::readout_eligible(*p, d_out)) return 0;
+  skv_problem q = *p;
+  q.delta_f32 = 0;
+  return round256(skv_scratch_bytes(&q, SKV_OP_FORWARD)) + round256((size_t)p->N * tc::readout_delta_pitch(*p) * 2) +
+         tc::readout_image_bytes(*p, d_out);
+}
+
+int skv_feature_readout_forward(const skv_problem* p, const void* z, int64_t z_stride, const void* C,
+                                const void* w_out, int64_t w_stride, int64_t d_out, void* y, int64_t y_stride,
+                                void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+  LaunchCtx c;
+  if (int e = make_ctx(p, stream, status, &c)) return e;
+  if (d_out < 1) return SKV_ERR_SHAPE;
+  if (!tc::readout_eligible(*p, d_out)) return SKV_ERR_UNSUPPORTED;
+  if (p->N == 0) return SKV_OK;
+  if (!z || !C || !w_out || !y) return SKV_ERR_NULL;
+  if (z_stride < p->h || w_stride < p->h + p->r || y_stride < d_out) return SKV_ERR_SHAPE;
+  if (!aligned(z, 16) || !aligned(w_out, 16) || !aligned(y, 16) || z_stride % 8 || w_stride % 8 || y_stride % 8)
+    return SKV_ERR_ALIGN;
+  if (!scratch || !aligned(scratch, 256) || scratch_bytes < skv_readout_scratch_bytes(p, d_out)) return SKV_ERR_SCRATCH;
+  skv_problem q = *p;
+  q.delta_f32 = 0;
+  const size_t fwd_bytes = round256(skv_scratch_bytes(&q, SKV_OP_FORWARD));
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+  void* delta = base + fwd_bytes;
+  const int64_t dp = tc::readout_delta_pitch(*p);
+  void* wimg = base + fwd_bytes + round256((size_t)p->N * dp * 2);
+  if (dp != p->r && cudaMemsetAsync(delta, 0, (size_t)p->N * dp * 2, c.stream) != cudaSuccess) return SKV_ERR_LAUNCH;
+  if (int e = skv_feature_forward(&q, z, z_stride, C, nullptr, 0, delta, dp, scratch, fwd_bytes, status, stream))
+    return e;
+  return tc::readout(c, z, z_stride, delta, w_out, w_stride, d_out, y, y_stride, wimg);
 }
 
 int skv_knot_index(const skv_problem* p, const void* z, int64_t z_stride, int32_t* bins, void* stream) {

@@ -175,6 +175,40 @@ def feature_forward(z, C, grid_lo, grid_hi, G, activation="relu_sq", lambda_scal
     return result
 
 
+def feature_readout_forward(z, C, W_out, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0):
+    """``y = [phi(z); lambda*delta] @ W_out.T`` as ``[N, d_out]`` without the feature in memory.
+
+    bf16 only (``z``, ``C`` and ``W_out`` are cast as the reference's wrapper casts them,
+    src/sparsespline_ffn/cuda_ext/__init__.py:626-632); ``W_out`` is ``[d_out, h + r]``, the layout of
+    ``torch.nn.Linear.weight``.  Forward only."""
+    lib = _lib.load()
+    if not (z.is_cuda and C.is_cuda and W_out.is_cuda):
+        raise RuntimeError("CUDA-only")
+    z = z if z.dtype == torch.bfloat16 else z.to(torch.bfloat16)
+    C = C if C.dtype == torch.bfloat16 else C.to(torch.bfloat16)
+    W_out = W_out if W_out.dtype == torch.bfloat16 else W_out.to(torch.bfloat16)
+    if activation not in ("relu_sq", "identity"):
+        raise ValueError(f"unsupported activation: {activation}")
+    p = _problem(z, C, grid_lo, grid_hi, G, activation, lambda_scale, "auto")
+    if W_out.dim() != 2 or W_out.shape[1] != p.h + p.r:
+        raise ValueError(f"W_out cols {tuple(W_out.shape)[-1]} != H+R={p.h + p.r}")
+    z, C, W_out = z.contiguous(), C.contiguous(), W_out.contiguous()
+    d_out = W_out.shape[0]
+    with torch.cuda.device(z.device):
+        y = torch.empty((p.N, d_out), dtype=torch.bfloat16, device=z.device)
+        need = int(lib.skv_readout_scratch_bytes(ctypes.byref(p), d_out))
+        if need == 0:
+            raise ValueError(f"the fused read-out needs h, r and d_out to be multiples of 8; got h={p.h}, r={p.r}, "
+                             f"d_out={d_out}")
+        scratch = torch.empty(need, dtype=torch.uint8, device=z.device)
+        code = lib.skv_feature_readout_forward(
+            ctypes.byref(p), _ptr(z), z.stride(0), _ptr(C), _ptr(W_out), W_out.stride(0), d_out, _ptr(y), y.stride(0),
+            _ptr(scratch), need, _ptr(status_word(z.device)),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(code)
+    return y
+
+
 def feature_backward(z, C, grad_out, grid_lo, grid_hi, G, activation="relu_sq", lambda_scale=1.0,
                      with_base=True, need_dz=True, need_dC=True, impl="auto", cast_dC=True, dz_f32=False,
                      spline_order: int = 2):

@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol(lib):
 
 
 def test_abi_version_and_error_strings(lib):
-    assert lib.skv_abi_version() == 3
+    assert lib.skv_abi_version() == 4
     for code in range(0, -8, -1):
         assert lib.skv_error_string(code)
     assert b"unknown" in lib.skv_error_string(-99)
