@@ -446,6 +446,7 @@ def main():
         extra = dict(
             key_sharded=extra_key_sharded(torch, dist, ops, sharded, cfg, rank, world, dev, timed),
             sweep=extra_sweep(torch, ops, cfg, rank, dev, timed),
+            readout=extra_readout(torch, ops, cfg, rank, dev, timed),
             stack7=extra_stack7(torch, dist, sharded, flash_spline_feature, cfg, kern, rank, world, dev, timed))
         ops.check_status(dev)
 
@@ -591,6 +592,42 @@ def extra_sweep(torch, ops, cfg, rank, dev, timed, N=131072, steps=5):
                         tokens_per_s=N / ((f_ms + b_ms) * 1e-3),
                         dense_equiv_tflops=round(3 * flops / ((f_ms + b_ms) * 1e-3) / 1e12, 1)))
         del C, go
+    return out
+
+
+def extra_readout(torch, ops, cfg, rank, dev, timed, steps=10):
+    """Forward followed by the read-out projection y = f W_out^T at the d20 shape (d_out = h / 4) on
+    this GPU: the fused entry point (delta-only feature kernels + this library's tcgen05 GEMM with the
+    activation applied to the z tile in shared memory; f is never written) beside the two-step path
+    (feature kernels + a torch matmul, i.e. the cuBLAS GEMM)."""
+    N, h, r, G = cfg["N"], cfg["h"], cfg["r"], cfg["G"]
+    lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]
+    D = h // 4
+    gen = torch.Generator(device=dev).manual_seed(777 + rank)
+    z = (torch.randn(N, h, generator=gen, device=dev) * cfg["z_std"]).to(torch.bfloat16)
+    C = (torch.randn(h, G + 2, r, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+    W = (torch.randn(D, h + r, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+    Wt = W.t()
+    out = {}
+    for act in ("relu_sq", "identity"):
+        fused = lambda: ops.feature_readout_forward(z, C, W, lo, hi, G, act, lam)
+        two_step = lambda: ops.feature_forward(z, C, lo, hi, G, act, lam) @ Wt
+        delta_only = lambda: ops.feature_forward(z, C, lo, hi, G, act, lam, with_base=False)
+        feature = lambda: ops.feature_forward(z, C, lo, hi, G, act, lam)
+        ms = {}
+        for name, fn in (("fused", fused), ("two_step", two_step), ("delta_only", delta_only), ("feature", feature)):
+            for _ in range(3):
+                fn()
+            ms[name] = timed(fn, steps) / steps
+        y1, y2 = fused().double(), two_step().double()
+        flops = 2.0 * N * (h + r) * D
+        gemm_ms = ms["fused"] - ms["delta_only"]
+        out[act] = dict(N=N, d_out=D, fused_ms=round(ms["fused"], 4), two_step_ms=round(ms["two_step"], 4),
+                        delta_only_ms=round(ms["delta_only"], 4), feature_ms=round(ms["feature"], 4),
+                        readout_gemm_ms=round(gemm_ms, 4), library_gemm_ms=round(ms["two_step"] - ms["feature"], 4),
+                        readout_gemm_tflops=round(flops / (gemm_ms * 1e-3) / 1e12, 1),
+                        rel_norm_vs_two_step=float((y1 - y2).norm() / y2.norm()))
+        del y1, y2
     return out
 
 

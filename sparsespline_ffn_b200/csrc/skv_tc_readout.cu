@@ -21,7 +21,10 @@
 // Three stages of (A 32 KB + B 32 KB).  Tiles that share their 256 tokens are adjacent in the walk, so the
 // z tile is read from HBM once and from L2 by the other D/256 - 1 CTAs.
 // (Loading the z tile with ordinary 16-byte loads into registers instead cost 37 L1 wavefronts per
-// load instruction and left the kernel bound by the load/store unit at 1.23 ms for the d20 shape.)
+// load instruction and left the kernel bound by the load/store unit at 1.23 ms for the d20 shape,
+// against 0.66 ms with the TMA load.  Six stages of 32 columns with the 64-byte swizzle were no faster
+// than three of 64 and doubled the L2 traffic; squaring one K step (16 columns) at a time, with a barrier
+// per step so that its MMAs start early, was slower: 0.71 against 0.68 ms.)
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -34,22 +37,20 @@ constexpr int32_t kStatusTimeoutReadout = 0x10;
 
 namespace {
 
-constexpr int kRoStages = 3;
-constexpr uint32_t kRoABytes = 256 * 64 * 2;     // one A stage: 256 tokens x 64 K
-constexpr uint32_t kRoBBytes = 256 * 64 * 2;     // one B stage: 256 outputs x 64 K
+constexpr int kRoK = 64;                         // K columns per stage: 64 (128-byte swizzle) or 32 (64-byte swizzle)
+constexpr int kRoStages = 192 / kRoK;            // 192 KB of stages
+constexpr uint32_t kRoABytes = 256 * kRoK * 2;   // one A stage: 256 tokens x kRoK
+constexpr uint32_t kRoBBytes = 256 * kRoK * 2;   // one B stage: 256 outputs x kRoK
 constexpr int kRoThreads = 320;
 
 struct RoParams {
-  const __nv_bfloat16* z;
-  int64_t zs;
-  const __nv_bfloat16* delta;    // [N][r], lambda applied
   const uint8_t* wimg;           // [n_tiles][ks][kRoBBytes]
   __nv_bfloat16* y;
   int64_t ys;
   int64_t N;
   int h, r, D;
-  int ks_z;                      // stages that read z: ceil(h / 64)
-  int ks;                        // all stages: ks_z + ceil(r / 64)
+  int ks_z;                      // stages that read z: ceil(h / 32)
+  int ks;                        // all stages: ks_z + ceil(r / 32)
   int n_tiles;                   // ceil(D / 256)
   int64_t tiles;                 // m_tiles * n_tiles
   int32_t* status;
@@ -57,13 +58,14 @@ struct RoParams {
 };
 
 // W[D][ws] (the layout of torch.nn.Linear.weight, columns [0,h) for act(z) and [h,h+r) for delta) ->
-// per (output tile, stage) a 256 x 64 K-major tile of 8 x 16-byte core matrices, [k core][n core][8 rows],
+// per (output tile, stage) a 256 x kRoK K-major tile of 8 x 16-byte core matrices, [k core][n core][8 rows],
 // zero where the tile reaches past D, h or r.
 __global__ void tc_pack_w_kernel(const __nv_bfloat16* __restrict__ W, int64_t ws, int D, int h, int r, int ks_z, int ks,
                                  int64_t chunks, uint4* __restrict__ img) {
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(idx & 2047);
-    const int64_t ts = idx >> 11;
+    constexpr int kPer = (int)(kRoBBytes / 16);
+    const int c = (int)(idx % kPer);
+    const int64_t ts = idx / kPer;
     const int s = (int)(ts % ks);
     const int64_t nt = ts / ks;
     const int kc = c >> 8, nc = (c >> 3) & 31, row = c & 7;
@@ -71,10 +73,10 @@ __global__ void tc_pack_w_kernel(const __nv_bfloat16* __restrict__ W, int64_t ws
     bool ok = n < D;
     int64_t k;
     if (s < ks_z) {
-      k = (int64_t)s * 64 + kc * 8;
+      k = (int64_t)s * kRoK + kc * 8;
       ok = ok && k < h;
     } else {
-      const int kd = (s - ks_z) * 64 + kc * 8;
+      const int kd = (s - ks_z) * kRoK + kc * 8;
       ok = ok && kd < r;
       k = (int64_t)h + kd;
     }
@@ -105,7 +107,7 @@ template <bool RELU>
 __global__ void __launch_bounds__(kRoThreads, 1)
     tc_readout_kernel(const RoParams P, const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_d) {
   extern __shared__ uint8_t smem_raw[];
-  // the swizzled A stages need 1024-byte alignment
+  // the swizzled A stages need 512-byte alignment (1024 keeps room for the 128-byte mode)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* a_base = smem;
   uint8_t* b_base = smem + kRoStages * kRoABytes;
@@ -147,12 +149,14 @@ __global__ void __launch_bounds__(kRoThreads, 1)
           const uint32_t st = it % kRoStages;
           if (mbar_wait(full + st, (it / kRoStages) & 1u, wc)) { drain = true; break; }
           if (s < P.ks_z) {
+            // elementwise, so the swizzled layout does not matter: 16-byte chunk j * 256 + tid of the stage
+            constexpr int kPerThread = (int)(kRoABytes / 4096);
             const uint32_t src = smem_u32(a_base + st * kRoABytes) + (uint32_t)tid * 16u;
-            uint4 v[8];
+            uint4 v[kPerThread];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = lds128(src + (uint32_t)j * 4096u);
+            for (int j = 0; j < kPerThread; ++j) v[j] = lds128(src + (uint32_t)j * 4096u);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kPerThread; ++j) {
               v[j].x = relu_sq_bf2(v[j].x); v[j].y = relu_sq_bf2(v[j].y);
               v[j].z = relu_sq_bf2(v[j].z); v[j].w = relu_sq_bf2(v[j].w);
               sts128(src + (uint32_t)j * 4096u, v[j]);
@@ -192,9 +196,10 @@ __global__ void __launch_bounds__(kRoThreads, 1)
   } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      // A: K-major tile with 128-byte rows and 128-byte swizzle (8-row groups 1024 bytes apart); a K step
-      // of 16 elements advances the start address by 32 bytes inside the swizzled row.
-      const uint32_t a_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      // A: K-major tile whose rows are one swizzle span (128 or 64 bytes) long, 8-row groups 8 rows apart;
+      // a K step of 16 elements advances the start address by 32 bytes inside the swizzled row.
+      constexpr uint32_t kRowBytes = kRoK * 2;
+      const uint32_t a_hi = ((8u * kRowBytes) >> 4) | (1u << 14) | ((kRoK == 64 ? 2u : 4u) << 29);
       const uint32_t b_hi = desc_hi(128u);
       constexpr uint32_t idesc = instr_desc(1, 1, 0, 0, 128, 256);
       uint32_t it = 0, ti = 0;
@@ -208,14 +213,14 @@ __global__ void __launch_bounds__(kRoThreads, 1)
           drain = mbar_wait((RELU ? ready : full) + st, ph, wc);
           if (drain) break;
           tc_fence_after();
-          int nk = 4;
-          if (s >= P.ks_z) nk = min(4, (P.r - (s - P.ks_z) * 64 + 15) / 16);
+          int nk = kRoK / 16;
+          if (s >= P.ks_z) nk = min(kRoK / 16, (P.r - (s - P.ks_z) * kRoK + 15) / 16);
           uint32_t a_lo = ((smem_u32(a_base + st * kRoABytes) >> 4) & 0x3FFFu) | (1u << 16);
           uint32_t b_lo = desc_lo(smem_u32(b_base + st * kRoBBytes), 4096u);
           for (int k = 0; k < nk; ++k) {
             const uint32_t accf = (s | k) ? 1u : 0u;
             umma_f16_split(tmem_base, a_lo, a_hi, b_lo, b_hi, idesc, accf);                        // tokens 0-127
-            umma_f16_split(tmem_base + 256u, a_lo + (16384u >> 4), a_hi, b_lo, b_hi, idesc, accf);  // tokens 128-255
+            umma_f16_split(tmem_base + 256u, a_lo + ((128u * kRowBytes) >> 4), a_hi, b_lo, b_hi, idesc, accf);  // tokens 128-255
             a_lo += 32u >> 4;
             b_lo += 8192u >> 4;
           }
@@ -237,8 +242,8 @@ __global__ void __launch_bounds__(kRoThreads, 1)
           const uint32_t st = it % kRoStages;
           if (it >= kRoStages && mbar_wait(empty + st, ((it / kRoStages) - 1u) & 1u, wc)) { stop = true; break; }
           mbar_arrive_expect_tx(full + st, kRoABytes + kRoBBytes);
-          if (s < P.ks_z) tma_load_2d(a_base + st * kRoABytes, &map_z, s * 64, m0, full + st);
-          else tma_load_2d(a_base + st * kRoABytes, &map_d, (s - P.ks_z) * 64, m0, full + st);
+          if (s < P.ks_z) tma_load_2d(a_base + st * kRoABytes, &map_z, s * kRoK, m0, full + st);
+          else tma_load_2d(a_base + st * kRoABytes, &map_d, (s - P.ks_z) * kRoK, m0, full + st);
           bulk_g2s(b_base + st * kRoBBytes, src + (size_t)s * kRoBBytes, kRoBBytes, full + st);
         }
       }
@@ -271,17 +276,17 @@ PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
   return fn;
 }
 
-// Map of a [rows][cols] bf16 matrix with row pitch `pitch` elements; boxes of 256 rows x 64 columns,
-// 128-byte swizzle, zeros outside the matrix.
+// Map of a [rows][cols] bf16 matrix with row pitch `pitch` elements; boxes of 256 rows x kRoK columns,
+// the swizzle span of one row, zeros outside the matrix.
 bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch) {
   PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
   if (!enc) return false;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {pitch * 2};
-  const cuuint32_t box[2] = {64, 256};
+  const cuuint32_t box[2] = {kRoK, 256};
   const cuuint32_t es[2] = {1, 1};
   return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, kRoK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -293,12 +298,12 @@ bool readout_eligible(const skv_problem& p, int64_t D) {
 }
 
 size_t readout_image_bytes(const skv_problem& p, int64_t D) {
-  const size_t ks = (size_t)(p.h + 63) / 64 + (size_t)(p.r + 63) / 64;
+  const size_t ks = (size_t)(p.h + kRoK - 1) / kRoK + (size_t)(p.r + kRoK - 1) / kRoK;
   return (size_t)((D + 255) / 256) * ks * kRoBBytes;
 }
 
-// Row pitch (elements) of the delta buffer the GEMM reads: whole 64-column stages, pad columns zero.
-int64_t readout_delta_pitch(const skv_problem& p) { return (int64_t)((p.r + 63) / 64) * 64; }
+// Row pitch (elements) of the delta buffer the GEMM reads: whole stages of kRoK columns, pad columns zero.
+int64_t readout_delta_pitch(const skv_problem& p) { return (int64_t)((p.r + kRoK - 1) / kRoK) * kRoK; }
 
 // y = [act(z) | delta] * W^T; `delta` is [N][readout_delta_pitch()] bf16 with zero pad columns, `wimg`
 // has readout_image_bytes().
@@ -306,9 +311,6 @@ int readout(const LaunchCtx& c, const void* z, int64_t zs, const void* delta, co
             void* y, int64_t ys, void* wimg) {
   const skv_problem& p = c.p;
   RoParams P;
-  P.z = static_cast<const __nv_bfloat16*>(z);
-  P.zs = zs;
-  P.delta = static_cast<const __nv_bfloat16*>(delta);
   P.wimg = static_cast<const uint8_t*>(wimg);
   P.y = static_cast<__nv_bfloat16*>(y);
   P.ys = ys;
@@ -316,8 +318,8 @@ int readout(const LaunchCtx& c, const void* z, int64_t zs, const void* delta, co
   P.h = (int)p.h;
   P.r = (int)p.r;
   P.D = (int)D;
-  P.ks_z = (int)((p.h + 63) / 64);
-  P.ks = P.ks_z + (int)((p.r + 63) / 64);
+  P.ks_z = (int)((p.h + kRoK - 1) / kRoK);
+  P.ks = P.ks_z + (int)((p.r + kRoK - 1) / kRoK);
   P.n_tiles = (int)((D + 255) / 256);
   P.tiles = ((p.N + 255) / 256) * P.n_tiles;
   P.status = c.status;
