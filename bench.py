@@ -235,6 +235,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the parity and extra-configuration records")
     ap.add_argument("--fused-backward", action="store_true",
                     help="run dz and dC as one kernel where its plan fits (A/B against the default two kernels)")
+    ap.add_argument("--only-readout", action="store_true",
+                    help="print only the forward + read-out record (profiling of the read-out GEMM; one GPU)")
     ap.add_argument("--e2e-chunks", type=int, default=16, help="token chunks the end-to-end step is pipelined over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -265,6 +267,21 @@ def main():
     _lib.check(lib.skv_device_ok())
     if args.fused_backward:
         lib.skv_debug_set(_lib.SKV_DEBUG_FUSED_BACKWARD, 1)
+
+    if args.only_readout:
+        def timed_1gpu(fn, steps):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1)
+        rec = extra_readout(torch, ops, cfg, rank, dev, timed_1gpu, steps=max(1, args.steps))
+        ops.check_status(dev)
+        print(json.dumps(dict(readout=rec, config=cfg_json(cfg, world))), flush=True)
+        return
 
     N, d, h, G, r = cfg["N"], cfg["d"], cfg["h"], cfg["G"], cfg["r"]
     lo, hi, lam = cfg["grid_lo"], cfg["grid_hi"], cfg["lambda_scale"]

@@ -181,7 +181,8 @@ int skv_feature_forward_noalloc(const skv_problem *p, const void *z, int64_t z_s
  *                              in the caller's status word and the kernel returns by itself
  *   SKV_DEBUG_SKIP_FIRST_COPY  1: the forward's loader leaves out its first code-table copy, so
  *                              that a wait runs out although nothing is in flight (tests of the
- *                              time-out path); 0 restores normal operation
+ *                              time-out path); 2: the same for the first stage of the read-out
+ *                              GEMM; 0 restores normal operation
  *   SKV_DEBUG_FUSED_BACKWARD   1: run dz and dC as one kernel (dedicated warps per role in one
  *                              CTA) where its plan fits, instead of the two kernels used by
  *                              default; same results, measured no faster (A/B timing, tests) */

@@ -135,7 +135,8 @@ int skv_debug_set(int what, int64_t value) {
       skv::g_wait_cycles.store((long long)value, std::memory_order_relaxed);
       return SKV_OK;
     case SKV_DEBUG_SKIP_FIRST_COPY:
-      skv::g_skip_copy.store(value != 0, std::memory_order_relaxed);
+      if (value < 0 || value > 2) return SKV_ERR_UNSUPPORTED;
+      skv::g_skip_copy.store((int)value, std::memory_order_relaxed);
       return SKV_OK;
     case SKV_DEBUG_FUSED_BACKWARD:
       skv::g_fused_bwd.store(value == 1 ? 3 : (value == 2 ? 1 : (value == 3 ? 2 : 0)), std::memory_order_relaxed);

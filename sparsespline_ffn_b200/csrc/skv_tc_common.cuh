@@ -21,7 +21,8 @@ constexpr long long kDefaultWaitCycles = 4000000000LL;
 
 // Test hooks, set through skv_debug_set (host side, read at launch time).
 long long wait_cycle_limit();        // current limit of every bounded wait
-int debug_skip_copy();               // 1: the forward's loader leaves out its first code-table copy
+int debug_skip_copy();               // 1: the forward's loader leaves out its first code-table copy;
+                                     // 2: the read-out GEMM's loader leaves out its first stage
 int fused_backward_roles();          // 0: two kernels (default); 3: dz and dC as one kernel where its plan fits
                                      // (1 / 2: that kernel with only its dz / only its dC role, for timing)
 

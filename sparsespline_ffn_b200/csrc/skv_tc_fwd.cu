@@ -660,7 +660,7 @@ int forward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, void* 
   P.status = c.status;
   P.cstages = f.cstages;
   P.wait_cycles = wait_cycle_limit();
-  P.skip_copy = debug_skip_copy();
+  P.skip_copy = debug_skip_copy() == 1;
   // A: Phi tile, K-major; core matrices of 8 tokens x 8 k: 128 B apart along tokens, 2048 B along k
   P.a_lbo = 2048;
   P.a_sbo = 128;

@@ -55,6 +55,7 @@ struct RoParams {
   int64_t tiles;                 // m_tiles * n_tiles
   int32_t* status;
   long long wait_cycles;
+  int skip_copy;                 // test hook: the loader leaves out its first stage
 };
 
 // W[D][ws] (the layout of torch.nn.Linear.weight, columns [0,h) for act(z) and [h,h+r) for delta) ->
@@ -240,6 +241,7 @@ __global__ void __launch_bounds__(kRoThreads, 1)
         const int m0 = (int)((t / P.n_tiles) * 256);
         for (int s = 0; s < P.ks; ++s, ++it) {
           const uint32_t st = it % kRoStages;
+          if (it == 0 && P.skip_copy) continue;      // test hook: nothing ever completes full[0]
           if (it >= kRoStages && mbar_wait(empty + st, ((it / kRoStages) - 1u) & 1u, wc)) { stop = true; break; }
           mbar_arrive_expect_tx(full + st, kRoABytes + kRoBBytes);
           if (s < P.ks_z) tma_load_2d(a_base + st * kRoABytes, &map_z, s * kRoK, m0, full + st);
@@ -324,6 +326,7 @@ int readout(const LaunchCtx& c, const void* z, int64_t zs, const void* delta, co
   P.tiles = ((p.N + 255) / 256) * P.n_tiles;
   P.status = c.status;
   P.wait_cycles = wait_cycle_limit();
+  P.skip_copy = debug_skip_copy() == 2;
   CUtensorMap map_z, map_d;
   if (!make_map(&map_z, z, (uint64_t)p.N, (uint64_t)p.h, (uint64_t)zs) ||
       !make_map(&map_d, delta, (uint64_t)p.N, (uint64_t)readout_delta_pitch(p), (uint64_t)readout_delta_pitch(p)))

@@ -41,6 +41,30 @@ def test_a_wait_that_runs_out_sets_the_status_word_and_the_device_stays_usable()
     ops.check_status(z.device)
 
 
+def test_the_readout_gemm_drains_when_its_first_stage_never_arrives():
+    lib = _lib.load()
+    N, h, r, G, d_out = 512, 128, 32, 20, 256
+    z, C, _ = util.make_inputs(N, h, r, G, torch.bfloat16)
+    W = (torch.randn(d_out, h + r, device=z.device) * 0.04).to(torch.bfloat16)
+    ops.check_status(z.device)
+    assert lib.skv_debug_set(_lib.SKV_DEBUG_WAIT_CYCLES, 2_000_000) == 0
+    assert lib.skv_debug_set(_lib.SKV_DEBUG_SKIP_FIRST_COPY, 2) == 0          # the feature kernels run normally
+    try:
+        ops.feature_readout_forward(z, C, W, -3.0, 3.0, G, "relu_sq", 1.0)
+        torch.cuda.synchronize()
+    finally:
+        lib.skv_debug_set(_lib.SKV_DEBUG_SKIP_FIRST_COPY, 0)
+        lib.skv_debug_set(_lib.SKV_DEBUG_WAIT_CYCLES, 4_000_000_000)
+    assert int(ops.status_word(z.device).item()) == 0x10, "only the read-out GEMM's time-out bit should be set"
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        ops.check_status(z.device)
+    y = ops.feature_readout_forward(z, C, W, -3.0, 3.0, G, "relu_sq", 1.0)
+    f = ops.feature_forward(z, C, -3.0, 3.0, G, "relu_sq", 1.0)
+    ref = f.double() @ W.double().t()
+    assert float((y.double() - ref).norm() / ref.norm()) < 4e-3
+    ops.check_status(z.device)
+
+
 def test_debug_set_rejects_unknown_settings():
     lib = _lib.load()
     assert lib.skv_debug_set(99, 1) < 0
