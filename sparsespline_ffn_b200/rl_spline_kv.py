@@ -25,6 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import ops
 from .kernels.flash_spline_feature_autograd import FlashSplineDelta, FlashSplineFeature, SplineFeatureOfOrder
 
 
@@ -83,12 +84,18 @@ def _phi(z: torch.Tensor, name: str) -> torch.Tensor:
 class RLSplineKV(nn.Module):
     """One RL-Spline-KV feed-forward layer whose feature step runs on the sm_100a kernels."""
 
-    def __init__(self, cfg: RLSplineKVConfig, operator_dtype: torch.dtype | None = None) -> None:
+    def __init__(self, cfg: RLSplineKVConfig, operator_dtype: torch.dtype | None = None,
+                 fused_readout: bool = False) -> None:
         """``operator_dtype``: run the feature operator in this dtype whatever the dtype of the
         module (z and C are cast on entry, the result is cast back), e.g. ``torch.bfloat16`` for the
-        tensor-core kernels under float32 master weights and GEMMs; None keeps the dtype of ``K x``."""
+        tensor-core kernels under float32 master weights and GEMMs; None keeps the dtype of ``K x``.
+        ``fused_readout``: when no gradient is being recorded, the additive quadratic-spline graph with a
+        ``relu_sq`` or ``identity`` base computes ``W_out f`` through the fused read-out (bf16, the feature
+        tensor is never allocated; what the reference offers as ``spline_kv_fwd_fused_cuda``,
+        ``src/sparsespline_ffn/cuda_ext/__init__.py:617-647``)."""
         super().__init__()
         self.operator_dtype = operator_dtype
+        self.fused_readout = fused_readout
         if cfg.spline_order != 2 and (cfg.no_base or cfg.gating_mode == "multiplicative"):
             raise NotImplementedError("no_base and multiplicative gating require spline_order=2")
         self.cfg = cfg
@@ -144,6 +151,11 @@ class RLSplineKV(nn.Module):
         elif cfg.gating_mode == "multiplicative":
             delta = FlashSplineDelta.apply(z, C, lo, hi, G, lam, cfg.bwd_kernel)              # [N, r], carries lambda
             y = self.W_out((1.0 + self.W_d_proj(delta.to(out_dtype))) * _phi(z_full, cfg.activation))
+        elif (self.fused_readout and cfg.spline_order == 2 and cfg.activation in ("relu_sq", "identity")
+              and not torch.is_grad_enabled()):
+            y = ops.feature_readout_forward(z, C, self.W_out.weight, lo, hi, G, cfg.activation, lam).to(out_dtype)
+            if self.W_out.bias is not None:
+                y = y + self.W_out.bias
         elif cfg.spline_order == 1:
             f = SplineFeatureOfOrder.apply(z, C, lo, hi, G, cfg.activation, lam, 1)            # [N, h + r]
             y = self.W_out(f.to(out_dtype))

@@ -91,3 +91,22 @@ def test_zero_code_table_leaves_the_base_projection():
     y = ops.feature_readout_forward(z, torch.zeros_like(C), W, LO, HI, G, "relu_sq", 1.0)
     a = torch.where(z > 0, z * z, torch.zeros_like(z))
     _gates("base only", y, (a.double() @ W[:, :h].double().T).cpu().numpy())
+
+
+def test_module_inference_through_the_fused_readout():
+    from sparsespline_ffn_b200 import RLSplineKV, RLSplineKVConfig
+    torch.manual_seed(0)
+    cfg = RLSplineKVConfig(d=128, h_ratio=2.0, r=32, G=20, grid_lo=-5.0, grid_hi=5.0, lambda_scale=0.5,
+                           c_init_std=0.3, bias=True)
+    m = RLSplineKV(cfg).cuda().to(torch.bfloat16)
+    x = torch.randn(3, 100, 128, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        y_plain = m(x)
+        m.fused_readout = True
+        y_fused = m(x)
+    assert y_fused.shape == y_plain.shape and y_fused.dtype == y_plain.dtype
+    err = float((y_fused.double() - y_plain.double()).norm() / y_plain.double().norm())
+    assert err < 1e-2, err                        # two bf16 GEMM implementations of the same product
+    y_grad = m(x.requires_grad_(True))            # with autograd on, the module takes the operator path
+    y_grad.float().sum().backward()
+    assert m.C.grad is not None and x.grad is not None
