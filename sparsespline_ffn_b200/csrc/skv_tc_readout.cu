@@ -89,7 +89,7 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// Tiled TMA load (no multicast) of one box of `map` at element coordinates (x, y) into this CTA's shared
+// Tiled TMA load, to this CTA alone, of one box of `map` at element coordinates (x, y) into this CTA's shared
 // memory; x * 2 bytes is a multiple of 16 at every call site (x is a multiple of 64).
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
