@@ -24,7 +24,11 @@
 // load instruction and left the kernel bound by the load/store unit at 1.23 ms for the d20 shape,
 // against 0.66 ms with the TMA load.  Six stages of 32 columns with the 64-byte swizzle were no faster
 // than three of 64 and doubled the L2 traffic; squaring one K step (16 columns) at a time, with a barrier
-// per step so that its MMAs start early, was slower: 0.71 against 0.68 ms.)
+// per step so that its MMAs start early, was slower: 0.71 against 0.68 ms.  So was a ReLU^2 variant with
+// the squared tile in tensor memory (128-token tiles, accumulator in 256 columns, A ring in the rest; no
+// stores back to shared memory and no A reads from it): 0.72 ms, because a 128 x 256 tile needs 48 KB
+// from L2 per 4.2 MFLOP against 64 KB per 8.4 MFLOP here, and both kernels take in about 90 GB/s per
+// SM, which looks like the limit of the L2-to-SM path.)
 #include <cuda.h>
 #include <cudaTypedefs.h>
 

@@ -110,3 +110,49 @@ def test_module_inference_through_the_fused_readout():
     y_grad = m(x.requires_grad_(True))            # with autograd on, the module takes the operator path
     y_grad.float().sum().backward()
     assert m.C.grad is not None and x.grad is not None
+
+
+def test_empty_input_and_unsupported_shapes():
+    z, C, W = (t.cuda() for t in _inputs(0, 64, 16, 20, 64, seed=1))
+    y = ops.feature_readout_forward(z, C, W, LO, HI, 20, "relu_sq", 1.0)
+    assert y.shape == (0, 64)
+    z, C, W = (t.cuda() for t in _inputs(8, 64, 16, 20, 60, seed=1))      # d_out not a multiple of 8
+    with pytest.raises(ValueError, match="multiples of 8"):
+        ops.feature_readout_forward(z, C, W, LO, HI, 20, "relu_sq", 1.0)
+    ops.check_status(z.device)
+
+
+def test_strided_inputs_through_the_c_abi():
+    """Row strides wider than the rows (z a column block of a wider matrix, y into a wider output)."""
+    import ctypes
+    from sparsespline_ffn_b200 import _lib
+    lib = _lib.load()
+    N, h, r, G, d_out = 300, 128, 32, 20, 136
+    z, C, W = (t.cuda() for t in _inputs(N, h, r, G, d_out, seed=9))
+    zwide = torch.zeros(N, h + 64, dtype=torch.bfloat16, device="cuda")
+    zwide[:, 32:32 + h] = z
+    zv = zwide[:, 32:32 + h]
+    Wwide = torch.zeros(d_out, h + r + 8, dtype=torch.bfloat16, device="cuda")
+    Wwide[:, :h + r] = W
+    ywide = torch.full((N, d_out + 24), 7.0, dtype=torch.bfloat16, device="cuda")
+    p = ops._problem(zv, C, LO, HI, G, "relu_sq", 1.0, "auto")
+    need = int(lib.skv_readout_scratch_bytes(ctypes.byref(p), d_out))
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    vp = ctypes.c_void_p
+    code = lib.skv_feature_readout_forward(
+        ctypes.byref(p), vp(zv.data_ptr()), zwide.stride(0), vp(C.data_ptr()), vp(Wwide.data_ptr()), Wwide.stride(0),
+        d_out, vp(ywide.data_ptr()), ywide.stride(0), vp(scratch.data_ptr()), need,
+        vp(ops.status_word(z.device).data_ptr()), vp(torch.cuda.current_stream().cuda_stream))
+    assert code == 0, lib.skv_error_string(code)
+    torch.cuda.synchronize()
+    ops.check_status(z.device)
+    f = ops.feature_forward(z, C, LO, HI, G, "relu_sq", 1.0)
+    _gates("strided", ywide[:, :d_out], (f.double() @ W.double().T).cpu().numpy())
+    assert bool((ywide[:, d_out:] == 7.0).all())                          # nothing written past d_out
+    # scratch one byte short, and a misaligned z, are refused
+    assert lib.skv_feature_readout_forward(
+        ctypes.byref(p), vp(zv.data_ptr()), zwide.stride(0), vp(C.data_ptr()), vp(Wwide.data_ptr()), Wwide.stride(0),
+        d_out, vp(ywide.data_ptr()), ywide.stride(0), vp(scratch.data_ptr()), need - 1, None, None) == -5
+    assert lib.skv_feature_readout_forward(
+        ctypes.byref(p), vp(zv.data_ptr() + 2), zwide.stride(0), vp(C.data_ptr()), vp(Wwide.data_ptr()),
+        Wwide.stride(0), d_out, vp(ywide.data_ptr()), ywide.stride(0), vp(scratch.data_ptr()), need, None, None) == -4
