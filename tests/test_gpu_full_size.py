@@ -100,3 +100,27 @@ def test_other_ranks_and_grids_at_full_key_count(r, G):
     f0 = ops.feature_forward(z, torch.zeros_like(C), LO, HI, G, "relu_sq", 0.25)
     assert torch.count_nonzero(f0[:, H:]) == 0
     ops.check_status(z.device)
+
+
+def test_fused_readout_properties_and_sampled_parity(data):
+    """y = [phi(z); lambda*delta] W_out^T at d_out = h / 4 without the feature tensor: determinism, exact
+    doubling in W_out (a power of two commutes with every rounding), independence of the tokens from one
+    another (a reversed token order gives the reversed rows, bit for bit, although every token lands in
+    another tile and lane), the feature followed by a float64 product on a token subset."""
+    z, C, _ = data
+    D = H // 4
+    g = torch.Generator(device="cuda").manual_seed(8)
+    W = (torch.randn(D, H + R, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    y = ops.feature_readout_forward(z, C, W, LO, HI, G, "relu_sq", 1.0)
+    assert y.shape == (N, D)
+    assert torch.equal(y, ops.feature_readout_forward(z, C, W, LO, HI, G, "relu_sq", 1.0))
+    assert torch.equal(ops.feature_readout_forward(z, C, W * 2, LO, HI, G, "relu_sq", 1.0).float(), 2 * y.float())
+    yr = ops.feature_readout_forward(z.flip(0).contiguous(), C, W, LO, HI, G, "relu_sq", 1.0)
+    assert torch.equal(yr.flip(0), y)
+    idx = torch.randperm(N, generator=torch.Generator().manual_seed(2))[:1024].cuda()
+    f = ops.feature_forward(z[idx].contiguous(), C, LO, HI, G, "relu_sq", 1.0)
+    ref = f.double() @ W.double().t()
+    err = (y[idx].double() - ref)
+    assert float(err.norm() / ref.norm()) < 4e-3
+    assert float(err.abs().max() / ref.abs().max()) < 8e-3
+    ops.check_status(z.device)
