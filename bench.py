@@ -260,7 +260,7 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    bind_to_gpu_numa_node(local_rank)
+    local_cores = bind_to_gpu_numa_node(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
@@ -447,6 +447,7 @@ def main():
         d2h = fh.numel() * 2 + dzh.numel() * 2 + dCh.numel() * 2
         e2e = dict(value=world * N / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
                    d2h_bytes_per_step=d2h, ms_per_step=e2e_ms, token_chunks=NCH,
+                   host_cores_local_to_gpu=(len(local_cores) if local_cores else 0),
                    bound="host link: every rank streams its inputs and outputs through the host's PCIe root and "
                          "memory, so this figure does not scale with the GPU count; `value` is the device-side one")
         ops.check_status(dev)
