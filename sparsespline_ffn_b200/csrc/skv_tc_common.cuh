@@ -385,6 +385,57 @@ __device__ __forceinline__ void phi_pair_words(float zz, const GridParams& g, ui
   wp = k.tbits >> 1;
 }
 
+// phi_pair_words for the two keys held in one packed bf16 word (low half = first key), with the
+// float32 arithmetic issued as two-wide instructions (add / sub / mul / fma .f32x2 of sm_100: each half
+// is the same IEEE operation with the same rounding as the scalar instruction, so every result is bit
+// for bit that of phi_pair_words).
+__device__ __forceinline__ unsigned long long f2_pack(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ void phi_pair_words2(uint32_t zw, const GridParams& g, uint32_t (&x0)[2], uint32_t (&x1)[2],
+                                                uint32_t (&wp)[2]) {
+  unsigned long long v, u2, t2, tau2, omt2, b0, b2, b1;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(f2_pack(bf_lo(zw), bf_hi(zw))), "l"(f2_pack(g.lo, g.lo)));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(u2) : "l"(v), "l"(f2_pack(g.scale, g.scale)), "l"(0ull));
+  float ua, ub;
+  f2_unpack(u2, ua, ub);
+  const float hma = __float_as_uint(ua) <= __float_as_uint(g.Gf) ? 0.5f : 0.0f;
+  const float hmb = __float_as_uint(ub) <= __float_as_uint(g.Gf) ? 0.5f : 0.0f;
+  const unsigned long long uc2 = f2_pack(fminf(fmaxf(ua, 0.0f), g.Gm1f), fminf(fmaxf(ub, 0.0f), g.Gm1f));
+  const unsigned long long big2 = f2_pack(8388608.0f, 8388608.0f), hm2 = f2_pack(hma, hmb);
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(t2) : "l"(uc2), "l"(big2));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(t2), "l"(big2));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(tau2) : "l"(uc2), "l"(v));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(omt2) : "l"(f2_pack(1.0f, 1.0f)), "l"(tau2));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(hm2), "l"(omt2));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(b0) : "l"(v), "l"(omt2));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(hm2), "l"(tau2));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(b2) : "l"(v), "l"(tau2));
+  asm("add.rn.f32x2 %0, %1, %1;" : "=l"(v) : "l"(hm2));                                    // 2 * hm, exact
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(b0), "l"(f2_pack(-1.0f, -1.0f)), "l"(v));  // 2 hm - B0, one rounding
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(b1) : "l"(v), "l"(b2));
+  float ta, tb, B0a, B0b, B1a, B1b, B2a, B2b;
+  f2_unpack(t2, ta, tb);
+  f2_unpack(b0, B0a, B0b);
+  f2_unpack(b1, B1a, B1b);
+  f2_unpack(b2, B2a, B2b);
+  const uint32_t tba = __float_as_uint(ta), tbb = __float_as_uint(tb);
+  const uint32_t p01a = pack_h2(B0a, B1a), p2a = pack_h2(B2a, 0.0f);
+  const uint32_t p01b = pack_h2(B0b, B1b), p2b = pack_h2(B2b, 0.0f);
+  const uint32_t sha = (tba & 1u) << 4, shb = (tbb & 1u) << 4;
+  x0[0] = p01a << sha;
+  x1[0] = __funnelshift_l(p01a, p2a, sha);
+  wp[0] = tba >> 1;
+  x0[1] = p01b << shb;
+  x1[1] = __funnelshift_l(p01b, p2b, shb);
+  wp[1] = tbb >> 1;
+}
+
 // Store N consecutive 32-bit columns of this thread's tensor-memory lane (lane = 32 * (warp % 4) + lane id).
 template <int N> __device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t* w);
 template <> __device__ __forceinline__ void tmem_st<1>(uint32_t taddr, const uint32_t* w) {

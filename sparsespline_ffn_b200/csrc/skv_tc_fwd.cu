@@ -358,12 +358,18 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
         // issued first, the select chains of the other keys run while those loads are in flight,
         // and the staged rows are written to tensor memory last.
         uint32_t Ws[NSTH > 0 ? NSTH : 1][HLP];
+        // knot interval and weights of the half's four keys, two keys (one packed z word) at a time
+        uint32_t kx0[kHalfKeys], kx1[kHalfKeys], kwp[kHalfKeys];
+#pragma unroll
+        for (int pq = 0; pq < kHalfKeys / 2; ++pq) {
+          uint32_t a0[2], a1[2], aw2[2];
+          phi_pair_words2(zw[half * (kHalfKeys / 2) + pq], P.g, a0, a1, aw2);   // rows past N read z = 0; their accumulator rows are never stored
+          kx0[2 * pq] = a0[0]; kx1[2 * pq] = a1[0]; kwp[2 * pq] = aw2[0];
+          kx0[2 * pq + 1] = a0[1]; kx1[2 * pq + 1] = a1[1]; kwp[2 * pq + 1] = aw2[1];
+        }
 #pragma unroll
         for (int qq = 0; qq < NSTH; ++qq) {
-          const int q = half * kHalfKeys + qq;
-          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
-          uint32_t x0, x1, wp;
-          phi_pair_words(zz, P.g, x0, x1, wp);   // rows past N read z = 0; their accumulator rows are never stored
+          const uint32_t x0 = kx0[qq], x1 = kx1[qq], wp = kwp[qq];
           const uint32_t pos = srow_biased + (wp << 7);
           sts32(pos, x0);
           sts32(pos + 128u, x1);
@@ -376,9 +382,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
 #pragma unroll
         for (int qq = NSTH; qq < kHalfKeys; ++qq) {
           const int q = half * kHalfKeys + qq;
-          const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
-          uint32_t x0, x1, wp;
-          phi_pair_words(zz, P.g, x0, x1, wp);
+          const uint32_t x0 = kx0[qq], x1 = kx1[qq], wp = kwp[qq];
           // Placement at word-pair granularity: wp = 2 * qd + s.  The two words land in pair qd as
           // (x0, x1) when s = 0, or as (0, x0) there and (x1, 0) in pair qd + 1 when s = 1.
           uint32_t W[HLP];
