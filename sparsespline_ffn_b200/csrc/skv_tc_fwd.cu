@@ -257,11 +257,15 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 // accumulator; with four groups (512 tokens per CTA, 16 producer warps) the other groups keep the
 // SM busy while one group waits for its MMAs.
 // ---------------------------------------------------------------------------------------------
-// Keys of each half chunk (of four) that are placed through the staging row; the others use
-// compare/select chains.  Two of four balances the load/store data pipe (staging traffic, the
-// tensor-memory stores and the strided global accesses: 72 % busy) against the ALU pipe (63 %)
-// at the d20 shape: 1 -> 1.07 ms, 2 -> 0.95 ms, 3 -> 0.99 ms, 4 -> 1.11 ms.
-constexpr int kStagedPerHalf = 2;
+// Keys of each half chunk (of four) that are placed through the staging row (load/store pipe); the
+// others are placed by multiplying with 0/1 masks in packed f16 arithmetic (FMA pipe).  When the
+// others used compare/select chains (ALU pipe, which issues at half rate and was 66 % busy) two of
+// four was the balance: 1 -> 1.07 ms, 2 -> 0.95 ms, 3 -> 0.99 ms, 4 -> 1.11 ms at the d20 shape.  With
+// the mask arithmetic: 0 -> 0.955 ms, 1 -> 0.900 ms, 2 -> 0.908 ms, 3 -> 0.984 ms.
+#ifndef SKV_NSTH
+#define SKV_NSTH 1
+#endif
+constexpr int kStagedPerHalf = SKV_NSTH;
 
 template <int GROUPS, int HL, int ACT, int NSTH>
 __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(const FwdParams P) {
@@ -387,10 +391,34 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           // (x0, x1) when s = 0, or as (0, x0) there and (x1, 0) in pair qd + 1 when s = 1.
           uint32_t W[HLP];
           const bool odd = (wp & 1u) != 0u;
-          const uint32_t qd = wp >> 1;
           const uint32_t y0 = odd ? 0u : x0, y1 = odd ? x0 : x1, y2 = odd ? x1 : 0u;
-          constexpr uint32_t kPairBias = kWordBias >> 1;
           constexpr int kLastPair = (HL - 2) >> 1;               // largest qd: bin <= L - 3
+#ifndef SKV_FWD_SELECT_CHAIN
+          // Each word is its value times a 0/1 mask in packed f16 arithmetic (x * 1 and x * 0 are exact
+          // for the non-negative finite weights, and at most one term of a sum is non-zero), so the
+          // placement runs on the FMA pipe instead of compare/select chains on the busier ALU pipe.
+          // qd (< 64) as the f16 value 1024 + qd has the bit pattern 0x6400 + qd.
+          const uint32_t q2 = (((wp >> 1) & 0x3fu) | 0x6400u) * 0x00010001u;
+          const __half2 qh = *reinterpret_cast<const __half2*>(&q2);
+          const __half2 h0 = *reinterpret_cast<const __half2*>(&y0), h1 = *reinterpret_cast<const __half2*>(&y1),
+                        h2 = *reinterpret_cast<const __half2*>(&y2);
+          __half2 m[HLP / 2];
+#pragma unroll
+          for (int i = 0; i < HLP / 2; ++i) {
+            const uint32_t ci2 = (0x6400u + (uint32_t)i) * 0x00010001u;
+            m[i] = i <= kLastPair ? __heq2(qh, *reinterpret_cast<const __half2*>(&ci2)) : __float2half2_rn(0.0f);
+          }
+#pragma unroll
+          for (int i = 0; i < HLP / 2; ++i) {
+            __half2 e = __hmul2(m[i], h0);
+            if (i > 0) e = __hfma2(m[i - 1], h2, e);
+            const __half2 o = __hmul2(m[i], h1);
+            W[2 * i] = *reinterpret_cast<const uint32_t*>(&e);
+            W[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&o);
+          }
+#else
+          const uint32_t qd = wp >> 1;
+          constexpr uint32_t kPairBias = kWordBias >> 1;
           bool hit[HLP / 2 + 1];
 #pragma unroll
           for (int i = 0; i < HLP / 2; ++i) hit[i] = i <= kLastPair && qd == kPairBias + (uint32_t)i;
@@ -400,6 +428,7 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
             W[2 * i] = hit[i] ? y0 : carry;
             W[2 * i + 1] = hit[i] ? y1 : 0u;
           }
+#endif
           tmem_st_words<HLP>(lane_addr + (uint32_t)(q * HLP), W);
         }
 #pragma unroll
