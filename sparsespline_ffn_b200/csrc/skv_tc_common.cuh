@@ -462,9 +462,10 @@ template <> __device__ __forceinline__ void tmem_st<16>(uint32_t taddr, const ui
       "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
       : "memory");
 }
-// HL (< 32) consecutive columns as the binary decomposition of HL into x16/x8/x4/x2/x1 stores.
+// HL (< 64) consecutive columns as the binary decomposition of HL into x16/x8/x4/x2/x1 stores.
 template <int HL> __device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t* w) {
   int o = 0;
+  if constexpr ((HL & 32) != 0) { tmem_st<16>(taddr, w); tmem_st<16>(taddr + 16, w + 16); o += 32; }
   if constexpr ((HL & 16) != 0) { tmem_st<16>(taddr + o, w + o); o += 16; }
   if constexpr ((HL & 8) != 0) { tmem_st<8>(taddr + o, w + o); o += 8; }
   if constexpr ((HL & 4) != 0) { tmem_st<4>(taddr + o, w + o); o += 4; }

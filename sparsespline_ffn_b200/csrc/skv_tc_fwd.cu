@@ -261,7 +261,8 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_forward_kernel(const 
 // others are placed by multiplying with 0/1 masks in packed f16 arithmetic (FMA pipe).  When the
 // others used compare/select chains (ALU pipe, which issues at half rate and was 66 % busy) two of
 // four was the balance: 1 -> 1.07 ms, 2 -> 0.95 ms, 3 -> 0.99 ms, 4 -> 1.11 ms at the d20 shape.  With
-// the mask arithmetic: 0 -> 0.955 ms, 1 -> 0.900 ms, 2 -> 0.908 ms, 3 -> 0.984 ms.
+// the mask arithmetic: 0 -> 0.955 ms, 1 -> 0.900 ms, 2 -> 0.908 ms, 3 -> 0.984 ms (0.917 / 0.890 / 0.903
+// for 0 / 1 / 2 once two keys share their tensor-memory stores).
 #ifndef SKV_NSTH
 #define SKV_NSTH 1
 #endif
@@ -361,7 +362,9 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
         // The first NSTH keys of the half go through the staging row: their stores and loads are
         // issued first, the select chains of the other keys run while those loads are in flight,
         // and the staged rows are written to tensor memory last.
-        uint32_t Ws[NSTH > 0 ? NSTH : 1][HLP];
+        // The words of two neighbouring keys are stored to tensor memory together (2 * HLP columns:
+        // one 16- and one 8-column store at HLP = 12 instead of two of each).
+        uint32_t WP[kHalfKeys / 2][2 * HLP];
         // knot interval and weights of the half's four keys, two keys (one packed z word) at a time
         uint32_t kx0[kHalfKeys], kx1[kHalfKeys], kwp[kHalfKeys];
 #pragma unroll
@@ -379,33 +382,32 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           sts32(pos + 128u, x1);
 #pragma unroll
           for (int i = 0; i < HLP; ++i)
-            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(Ws[qq][i]) : "r"(srow + (uint32_t)i * 128u) : "memory");
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(WP[qq >> 1][(qq & 1) * HLP + i]) : "r"(srow + (uint32_t)i * 128u) : "memory");
           sts32(pos, 0u);
           sts32(pos + 128u, 0u);
         }
 #pragma unroll
         for (int qq = NSTH; qq < kHalfKeys; ++qq) {
-          const int q = half * kHalfKeys + qq;
           const uint32_t x0 = kx0[qq], x1 = kx1[qq], wp = kwp[qq];
           // Placement at word-pair granularity: wp = 2 * qd + s.  The two words land in pair qd as
           // (x0, x1) when s = 0, or as (0, x0) there and (x1, 0) in pair qd + 1 when s = 1.
-          uint32_t W[HLP];
+          uint32_t* W = &WP[qq >> 1][(qq & 1) * HLP];
           const bool odd = (wp & 1u) != 0u;
           const uint32_t y0 = odd ? 0u : x0, y1 = odd ? x0 : x1, y2 = odd ? x1 : 0u;
           constexpr int kLastPair = (HL - 2) >> 1;               // largest qd: bin <= L - 3
-#ifndef SKV_FWD_SELECT_CHAIN
           // Each word is its value times a 0/1 mask in packed f16 arithmetic (x * 1 and x * 0 are exact
           // for the non-negative finite weights, and at most one term of a sum is non-zero), so the
           // placement runs on the FMA pipe instead of compare/select chains on the busier ALU pipe.
-          // qd (< 64) as the f16 value 1024 + qd has the bit pattern 0x6400 + qd.
-          const uint32_t q2 = (((wp >> 1) & 0x3fu) | 0x6400u) * 0x00010001u;
+          // wp >> 1 is (kKnotBias >> 2) + qd with qd < 64; times 0x10001 that is the f16 pair with bit
+          // patterns qd (low) and (kKnotBias >> 18) + qd (high): two ordinary, distinct-per-qd values.
+          const uint32_t q2 = (wp >> 1) * 0x00010001u;
           const __half2 qh = *reinterpret_cast<const __half2*>(&q2);
           const __half2 h0 = *reinterpret_cast<const __half2*>(&y0), h1 = *reinterpret_cast<const __half2*>(&y1),
                         h2 = *reinterpret_cast<const __half2*>(&y2);
           __half2 m[HLP / 2];
 #pragma unroll
           for (int i = 0; i < HLP / 2; ++i) {
-            const uint32_t ci2 = (0x6400u + (uint32_t)i) * 0x00010001u;
+            const uint32_t ci2 = (((kKnotBias >> 18) + (uint32_t)i) << 16) | (uint32_t)i;
             m[i] = i <= kLastPair ? __heq2(qh, *reinterpret_cast<const __half2*>(&ci2)) : __float2half2_rn(0.0f);
           }
 #pragma unroll
@@ -416,24 +418,12 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
             W[2 * i] = *reinterpret_cast<const uint32_t*>(&e);
             W[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&o);
           }
-#else
-          const uint32_t qd = wp >> 1;
-          constexpr uint32_t kPairBias = kWordBias >> 1;
-          bool hit[HLP / 2 + 1];
-#pragma unroll
-          for (int i = 0; i < HLP / 2; ++i) hit[i] = i <= kLastPair && qd == kPairBias + (uint32_t)i;
-#pragma unroll
-          for (int i = 0; i < HLP / 2; ++i) {
-            const uint32_t carry = (i > 0 && hit[i - 1]) ? y2 : 0u;
-            W[2 * i] = hit[i] ? y0 : carry;
-            W[2 * i + 1] = hit[i] ? y1 : 0u;
-          }
-#endif
-          tmem_st_words<HLP>(lane_addr + (uint32_t)(q * HLP), W);
+          if ((qq & 1) && (qq & ~1) >= NSTH)            // a pair of mask-placed keys is complete
+            tmem_st_words<2 * HLP>(lane_addr + (uint32_t)((half * kHalfKeys + (qq & ~1)) * HLP), WP[qq >> 1]);
         }
 #pragma unroll
-        for (int qq = 0; qq < NSTH; ++qq)
-          tmem_st_words<HLP>(lane_addr + (uint32_t)((half * kHalfKeys + qq) * HLP), Ws[qq]);
+        for (int pp = 0; 2 * pp < NSTH; ++pp)            // pairs with a staged key: their loads have landed by now
+          tmem_st_words<2 * HLP>(lane_addr + (uint32_t)((half * kHalfKeys + 2 * pp) * HLP), WP[pp]);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive_warp(full + grp * 2 + half);
