@@ -462,10 +462,20 @@ template <> __device__ __forceinline__ void tmem_st<16>(uint32_t taddr, const ui
       "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
       : "memory");
 }
+template <> __device__ __forceinline__ void tmem_st<32>(uint32_t taddr, const uint32_t* w) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]), "r"(w[9]),
+      "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]), "r"(w[16]), "r"(w[17]), "r"(w[18]),
+      "r"(w[19]), "r"(w[20]), "r"(w[21]), "r"(w[22]), "r"(w[23]), "r"(w[24]), "r"(w[25]), "r"(w[26]), "r"(w[27]),
+      "r"(w[28]), "r"(w[29]), "r"(w[30]), "r"(w[31])
+      : "memory");
+}
 // HL (< 64) consecutive columns as the binary decomposition of HL into x16/x8/x4/x2/x1 stores.
 template <int HL> __device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t* w) {
   int o = 0;
-  if constexpr ((HL & 32) != 0) { tmem_st<16>(taddr, w); tmem_st<16>(taddr + 16, w + 16); o += 32; }
+  if constexpr ((HL & 32) != 0) { tmem_st<32>(taddr, w); o += 32; }
   if constexpr ((HL & 16) != 0) { tmem_st<16>(taddr + o, w + o); o += 16; }
   if constexpr ((HL & 8) != 0) { tmem_st<8>(taddr + o, w + o); o += 8; }
   if constexpr ((HL & 4) != 0) { tmem_st<4>(taddr + o, w + o); o += 4; }
