@@ -389,18 +389,18 @@ struct DcParams {
 };
 
 // KCH = keys per chunk.  Two producer groups of 128 threads (thread = token of the group's tile).
-template <int KCH>
+template <int KCH, int HLC>
 __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int L = P.L, LR = P.LR, r = P.r;
+  const int L = P.L, LR = HLC ? 2 * HLC : P.LR, r = P.r;
   const uint32_t phi_bytes = (uint32_t)P.mtiles * 16u * 2048u;     // [m groups][16 token groups][8 tok][8 m]
   const uint32_t g_bytes = (uint32_t)(128 * r * 2);
   uint8_t* phi_base = smem;                                         // [2][phi_bytes]
   uint8_t* g_base = smem + 2 * (size_t)phi_bytes;                   // [2][g_bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(g_base + 2 * (size_t)g_bytes);
   uint64_t* pfull = bars;          // [2] producers -> MMA
-  uint64_t* pempty = pfull + 2;    // [2] MMA -> producers
-  uint64_t* gfull = pempty + 2;    // [2] TMA -> MMA
+  uint64_t* pempty = pfull + 2;    // [2][3] MMA -> producers, per 128-row tile
+  uint64_t* gfull = pempty + 6;    // [2] TMA -> MMA
   uint64_t* gempty = gfull + 2;    // [2] MMA -> TMA
   uint64_t* done = gempty + 2;     // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
@@ -419,10 +419,10 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(pfull + i, 4);
-      mbar_init(pempty + i, 1);
       mbar_init(gfull + i, 1);
       mbar_init(gempty + i, 1);
     }
+    for (int i = 0; i < 6; ++i) mbar_init(pempty + i, 1);
     mbar_init(done, 1);
     *abort_flag = 0;
     mbar_init_fence();
@@ -469,19 +469,28 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
           znext[i] = valid && in_h ? __ldg(reinterpret_cast<const uint4*>(zrow + (ch + 1) * KCH + i * 8))
                                    : make_uint4(0, 0, 0, 0);
         }
-        if (use > 0) mbar_wait(pempty + pg, (uint32_t)(use - 1) & 1u, wc);
-        if (have_saved) {
+        // The MMA thread releases a stage tile by tile (128 knot rows each); with the words per key
+        // known at compile time (HLC) a tile is waited for just before the first key that touches it,
+        // so this stage's first keys are written while the MMAs still read the later tiles of the
+        // previous use.  Otherwise all tiles are waited for first.
+        if (!HLC && use > 0)
+          for (int m = 0; m < P.mtiles; ++m) mbar_wait(pempty + pg * 3 + m, (uint32_t)(use - 1) & 1u, wc);
+        const int keys_left = P.h - (key0 + ch * KCH);         // keys of this chunk that exist
 #pragma unroll
-          for (int q = 0; q < KCH; ++q) {
+        for (int q = 0; q < KCH; ++q) {
+          if (HLC && use > 0) {
+            // tiles touched by words q * HLC .. (q + 1) * HLC - 1 (word w lies in tile w >> 6) that no
+            // earlier key touched
+            const int t_lo = q == 0 ? 0 : (((q * HLC - 1) >> 6) + 1), t_hi = ((q + 1) * HLC - 1) >> 6;
+#pragma unroll
+            for (int m = 0; m < 3; ++m)
+              if (m >= t_lo && m <= t_hi) mbar_wait(pempty + pg * 3 + m, (uint32_t)(use - 1) & 1u, wc);
+          }
+          if (have_saved) {
             sts32(row + (saved[q] & 0xffffu) * 4u, 0u);
             sts32(row + (saved[q] >> 16) * 4u, 0u);
           }
-          have_saved = false;
-        }
-        if (valid) {
-          const int keys_left = P.h - (key0 + ch * KCH);       // keys of this chunk that exist
-#pragma unroll
-          for (int q = 0; q < KCH; ++q) {
+          if (valid) {
             const uint4& zc = zq[q >> 3];
             const uint32_t zw[4] = {zc.x, zc.y, zc.z, zc.w};
             const int qq = q & 7;
@@ -493,8 +502,8 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
             sts32(row + wo1 * 4u, x1);
             saved[q] = wo0 | (wo1 << 16);
           }
-          have_saved = true;
         }
+        have_saved = valid;
         fence_async_smem();
         mbar_arrive_warp(pfull + pg);
       }
@@ -557,8 +566,8 @@ __global__ void __launch_bounds__(256 + 64, 1) tc_dc_kernel(const DcParams P) {
                 b_lo += 256u >> 4;
                 umma_f16_split(d_addr, a_lo, ab_hi, b_lo, ab_hi, idesc, 1u);
               }
+              umma_commit(pempty + pg * 3 + mt);
             }
-            umma_commit(pempty + pg);
           }
           if (drain) break;
         }
@@ -1321,11 +1330,16 @@ int backward(const LaunchCtx& c, const void* z, int64_t zs, const void* C, const
     dim3 grid((unsigned)dp.slabs, (unsigned)dp.splits);
     cudaError_t err;
     if (dp.kch == 16) {
-      err = cudaFuncSetAttribute(tc_dc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
-      if (err == cudaSuccess) tc_dc_kernel<16><<<grid, 320, dp.smem, c.stream>>>(P);
+      if (P.LR == 22) {
+        err = cudaFuncSetAttribute(tc_dc_kernel<16, 11>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
+        if (err == cudaSuccess) tc_dc_kernel<16, 11><<<grid, 320, dp.smem, c.stream>>>(P);
+      } else {
+        err = cudaFuncSetAttribute(tc_dc_kernel<16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
+        if (err == cudaSuccess) tc_dc_kernel<16, 0><<<grid, 320, dp.smem, c.stream>>>(P);
+      }
     } else {
-      err = cudaFuncSetAttribute(tc_dc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
-      if (err == cudaSuccess) tc_dc_kernel<8><<<grid, 320, dp.smem, c.stream>>>(P);
+      err = cudaFuncSetAttribute(tc_dc_kernel<8, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem);
+      if (err == cudaSuccess) tc_dc_kernel<8, 0><<<grid, 320, dp.smem, c.stream>>>(P);
     }
     note_launches(1);
     if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) { cudaGetLastError(); return SKV_ERR_LAUNCH; }
