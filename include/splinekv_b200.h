@@ -141,8 +141,8 @@ int skv_knot_index(const skv_problem *p, const void *z, int64_t z_stride, int32_
  *   w_out    [d_out, h + r] bf16, row stride w_stride elements (the layout of torch.nn.Linear.weight)
  *   y        [N, d_out] bf16 out, row stride y_stride
  * Needs dtype bf16, activation relu_sq or identity, h, r, d_out, the three row strides multiples of 8 and
- * 16-byte aligned pointers (else SKV_ERR_UNSUPPORTED / SKV_ERR_ALIGN).  Scratch:
- * skv_readout_scratch_bytes(p, d_out).  A bounded wait of the GEMM that runs out sets bit 0x10 of *status. */
+ * 16-byte aligned pointers (else SKV_ERR_UNSUPPORTED / SKV_ERR_ALIGN), N below 2^31 - 256.  Scratch:
+ * skv_readout_scratch_bytes(p, d_out) bytes at a 256-byte aligned address (else SKV_ERR_SCRATCH).  A bounded wait of the GEMM that runs out sets bit 0x10 of *status. */
 size_t skv_readout_scratch_bytes(const skv_problem *p, int64_t d_out);
 int skv_feature_readout_forward(const skv_problem *p, const void *z, int64_t z_stride, const void *C,
                                 const void *w_out, int64_t w_stride, int64_t d_out, void *y, int64_t y_stride,
