@@ -399,7 +399,8 @@ __global__ void __launch_bounds__(160 * GROUPS + 32, 1) tc_forward_ta_kernel(con
           // for the non-negative finite weights, and at most one term of a sum is non-zero), so the
           // placement runs on the FMA pipe instead of compare/select chains on the busier ALU pipe.
           // wp >> 1 is (kKnotBias >> 2) + qd with qd < 64; times 0x10001 that is the f16 pair with bit
-          // patterns qd (low) and (kKnotBias >> 18) + qd (high): two ordinary, distinct-per-qd values.
+          // patterns qd (low: a subnormal, or zero) and (kKnotBias >> 18) + qd (high): distinct per qd.
+          // f16 comparisons do not flush subnormals (this file is not built with a flush-to-zero flag).
           const uint32_t q2 = (wp >> 1) * 0x00010001u;
           const __half2 qh = *reinterpret_cast<const __half2*>(&q2);
           const __half2 h0 = *reinterpret_cast<const __half2*>(&y0), h1 = *reinterpret_cast<const __half2*>(&y1),
