@@ -124,28 +124,57 @@ struct DzParams {
 };
 
 
-// Tensor-memory loads of one key's S columns (LB blocks of 8 float32 columns of this warp's lanes).
-// The loads are issued without waiting; tmem_wait_key waits for all outstanding loads and ties
-// the destination registers to the wait so that no use can be scheduled ahead of it.
-template <int LB>
-__device__ __forceinline__ void tmem_ld_key(uint32_t taddr, uint32_t (&r)[LB][8]) {
-#pragma unroll
-  for (int blk = 0; blk < LB; ++blk)
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[blk][0]), "=r"(r[blk][1]), "=r"(r[blk][2]), "=r"(r[blk][3]), "=r"(r[blk][4]),
-                   "=r"(r[blk][5]), "=r"(r[blk][6]), "=r"(r[blk][7])
-                 : "r"(taddr + (uint32_t)blk * 8u)
-                 : "memory");
+// Tensor-memory loads of one key's S columns: the first NC of its LB blocks of 8 float32 columns of
+// this warp's lanes (the padding columns are never read: the kernel's time follows the bytes it moves
+// out of tensor memory, 4 * NC per pair).  The loads are issued without waiting; tmem_wait_key waits
+// for all outstanding loads and ties the destination registers to the wait so that no use can be
+// scheduled ahead of it.
+template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r);
+template <> __device__ __forceinline__ void tmem_ld_cols<8>(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
-template <int LB>
+template <> __device__ __forceinline__ void tmem_ld_cols<4>(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_cols<2>(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_cols<1>(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r[0]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// All 8 * LB columns of the key, in as few instructions as possible (a load instruction costs more
+// than the columns it moves: loading only the NC useful columns as 8 + 8 + 4 + 1 was slower, 1.16 ms
+// against 1.11 ms at the d20 shape).
+template <int LB, int NC>
+__device__ __forceinline__ void tmem_ld_key(uint32_t taddr, uint32_t (&r)[LB][8]) {
+  uint32_t* flat = &r[0][0];
+  int o = 0;
+#pragma unroll
+  for (int i = 0; i < LB / 2; ++i) { tmem_ld_cols<16>(taddr + (uint32_t)o, flat + o); o += 16; }
+  if constexpr ((LB & 1) != 0) tmem_ld_cols<8>(taddr + (uint32_t)o, flat + o);
+}
+template <int LB, int NC>
 __device__ __forceinline__ void tmem_wait_key(uint32_t (&r)[LB][8]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int blk = 0; blk < LB; ++blk)
-    asm volatile("" : "+r"(r[blk][0]), "+r"(r[blk][1]), "+r"(r[blk][2]), "+r"(r[blk][3]), "+r"(r[blk][4]),
-                      "+r"(r[blk][5]), "+r"(r[blk][6]), "+r"(r[blk][7])
-                 :
-                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) asm volatile("" : "+r"(r[blk][i]) : : "memory");
 }
 
 // S_0 + sum_m sat(uc - m) * S_{m+1} over the first NC of the 8*LB columns of one key.  Columns
@@ -260,14 +289,14 @@ __global__ void __launch_bounds__(128 * GROUPS + 64, 1) tc_dz_kernel(const DzPar
       float outv[kChunkKeys];
       mbar_wait(sfull + grp, (uint32_t)ci & 1u, wc);
       tc_fence_after();
-      tmem_ld_key<LB>(trow, bufa);
+      tmem_ld_key<LB, NC>(trow, bufa);
 #pragma unroll
       for (int q = 0; q < kChunkKeys; ++q) {
         // the loads of key q are in flight; wait, start the loads of key q+1, then do key q's math
-        if (q & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
+        if (q & 1) tmem_wait_key<LB, NC>(bufb); else tmem_wait_key<LB, NC>(bufa);
         if (q + 1 < kChunkKeys) {
-          if (q & 1) tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufa);
-          else tmem_ld_key<LB>(trow + (uint32_t)((q + 1) * LP), bufb);
+          if (q & 1) tmem_ld_key<LB, NC>(trow + (uint32_t)((q + 1) * LP), bufa);
+          else tmem_ld_key<LB, NC>(trow + (uint32_t)((q + 1) * LP), bufb);
         }
         const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
         // same u and the same single-comparison range test as knot_of
@@ -798,14 +827,14 @@ __global__ void __launch_bounds__(kBfThreads, 1) tc_bwd_fused_kernel(const BfPar
           uint32_t bufa[LB][8], bufb[LB][8];
           mbar_wait(sfull + pg * 2 + (use & 1), (uint32_t)(use >> 1) & 1u, wc);
           tc_fence_after();
-          tmem_ld_key<LB>(blk, bufa);
+          tmem_ld_key<LB, NC>(blk, bufa);
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             const int q = qt * 4 + q4;
-            if (q4 & 1) tmem_wait_key<LB>(bufb); else tmem_wait_key<LB>(bufa);
+            if (q4 & 1) tmem_wait_key<LB, NC>(bufb); else tmem_wait_key<LB, NC>(bufa);
             if (q4 + 1 < 4) {
-              if (q4 & 1) tmem_ld_key<LB>(blk + (uint32_t)((q4 + 1) * LP), bufa);
-              else tmem_ld_key<LB>(blk + (uint32_t)((q4 + 1) * LP), bufb);
+              if (q4 & 1) tmem_ld_key<LB, NC>(blk + (uint32_t)((q4 + 1) * LP), bufa);
+              else tmem_ld_key<LB, NC>(blk + (uint32_t)((q4 + 1) * LP), bufb);
             }
             const float zz = (q & 1) ? bf_hi(zw[q >> 1]) : bf_lo(zw[q >> 1]);
             const float u = __fmaf_rn(__fsub_rn(zz, P.g.lo), P.g.scale, 0.0f);
